@@ -68,6 +68,19 @@ SIGNATURES = {
     "dli_gemv_argmax_bf16": (_i, [_vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "dli_sample_bf16": (_i, [_vp, _i, _vp, _i, _i, _f, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
     "dli_decode_advance": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "dli_scalar_rmsnorm_f32": (_i, [_vp, _vp, _i, _i, _f, _f, _vp]),
+    "dli_postnorm_add_norm": (_i, [_vp, _vp, _vp, _i, _i, _f, _f, _f, _i, _vp]),
+    "dli_causal_conv_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "dli_gather_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dli_linear_any": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "dli_silu_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
+    "dli_attn_prep_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                  _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "dli_attn_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
+                             _i, _vp, _vp, _i, _vp]),
+    "dli_mlstm_ragged": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp,
+                              _f, _vp, _vp, _vp, _i, _vp]),
 }
 
 

@@ -29,6 +29,9 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "elementwise.cu",
     "sample.cu",
+    "ragged_rows.cu",
+    "attn_ragged.cu",
+    "mlstm.cu",
 ]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

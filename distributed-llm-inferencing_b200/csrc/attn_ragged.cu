@@ -1,0 +1,266 @@
+// Attention over a paged cache for a RAGGED step (rows of several sequences, a prompt's portion beside single
+// decoded tokens), with the options a layer can switch on independently:
+//   - per-head RMS norm of queries and keys (one weight vector of the head size, shared by the heads),
+//   - rotary positions on the first `rd` dimensions, INTERLEAVED pairs (2i, 2i+1), angles from a host-made fp32
+//     cos/sin table [positions, rd/2] (so any frequency scaling is the table's business),
+//   - rotated values: the value of position j is turned by j over all its pairs before it is cached, and a
+//     head's output at position i is turned back by -i,
+//   - key/value heads shared by groups of query heads, key size D and value size V independent,
+//   - a chunk mask (position i sees j <= i in its own chunk of `chunk` positions, counted from position 0) and/or
+//     a sliding window (j > i - window),
+//   - a sink: one more term exp(sink[h]) in the softmax denominator, without key or value,
+//   - an output gate: head h's output times sigmoid(gate[row, h]).
+// Scores, softmax weights and the accumulation are fp32; the cache holds E (bf16 or float).
+//
+// Step description as in ragged_rows.cu: row_ent[rows], ent[4 * n_ent] = (slot, first row, rows, first position);
+// page_table[slot * max_pages + p] is the page of positions p*page_size .. of the sequence in that slot.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dli {
+
+template <typename E> __device__ __forceinline__ float a_to_f(E v);
+template <> __device__ __forceinline__ float a_to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float a_to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename E> __device__ __forceinline__ E a_from_f(float v);
+template <> __device__ __forceinline__ float a_from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 a_from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+struct AttnPrep {
+  const int32_t* row_ent;
+  const int32_t* ent;
+  const int32_t* page_table;
+  int max_pages, page_size;
+  int H, G, D, V, rd;       // query heads, key/value heads, key size, value size, rotated dims of q/k
+  int ldp, q_off, k_off, v_off;  // packed projection row: stride and column offsets
+  const float* qn;          // [D] or NULL: weights of the query / key norm
+  const float* kn;
+  float eps;
+  const float* cos_qk;      // [positions, rd/2] or NULL (no rotation)
+  const float* sin_qk;
+  const float* cos_v;       // [positions, V/2] or NULL (values are cached as they are)
+  const float* sin_v;
+  int table_len;
+};
+
+// One CTA per row; each warp takes heads in turn: q heads -> qbuf (fp32, normed and rotated), key heads and value
+// heads -> the sequence's cache page.
+template <typename E>
+__global__ void __launch_bounds__(128)
+attn_prep_append_kernel(const E* __restrict__ proj, float* __restrict__ qbuf, E* __restrict__ kc, E* __restrict__ vc,
+                        AttnPrep a) {
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[a.row_ent[row]];
+  const int pos = e.w + (row - e.y);
+  const int page = a.page_table[(size_t)e.x * a.max_pages + pos / a.page_size], off = pos % a.page_size;
+  const E* pr = proj + (size_t)row * a.ldp;
+  for (int item = warp; item < a.H + 2 * a.G; item += 4) {
+    if (item < a.H + a.G) {
+      const bool is_q = item < a.H;
+      const int hh = is_q ? item : item - a.H;
+      const E* src = pr + (is_q ? a.q_off : a.k_off) + hh * a.D;
+      const float* nw = is_q ? a.qn : a.kn;
+      float r = 1.f;
+      if (nw) {
+        float ss = 0.f;
+        for (int c = lane; c < a.D; c += 32) { const float v = a_to_f(src[c]); ss += v * v; }
+        ss = warp_sum(ss);
+        r = 1.f / sqrtf(ss / a.D + a.eps);
+      }
+      float* qd = qbuf + ((size_t)row * a.H + hh) * a.D;
+      E* kd = kc + (((size_t)page * a.G + hh) * a.page_size + off) * a.D;
+      for (int i = lane; i < a.D / 2; i += 32) {
+        float u = a_to_f(src[2 * i]), v = a_to_f(src[2 * i + 1]);
+        if (nw) { u = u * r * nw[2 * i]; v = v * r * nw[2 * i + 1]; }
+        if (a.cos_qk && 2 * i < a.rd) {
+          const float c = a.cos_qk[(size_t)pos * (a.rd / 2) + i], s = a.sin_qk[(size_t)pos * (a.rd / 2) + i];
+          const float u2 = u * c - v * s, v2 = v * c + u * s;
+          u = u2; v = v2;
+        }
+        if (is_q) { qd[2 * i] = u; qd[2 * i + 1] = v; }
+        else { kd[2 * i] = a_from_f<E>(u); kd[2 * i + 1] = a_from_f<E>(v); }
+      }
+    } else {
+      const int g = item - a.H - a.G;
+      const E* src = pr + a.v_off + g * a.V;
+      E* vd = vc + (((size_t)page * a.G + g) * a.page_size + off) * a.V;
+      for (int i = lane; i < a.V / 2; i += 32) {
+        float u = a_to_f(src[2 * i]), v = a_to_f(src[2 * i + 1]);
+        if (a.cos_v) {
+          const float c = a.cos_v[(size_t)pos * (a.V / 2) + i], s = a.sin_v[(size_t)pos * (a.V / 2) + i];
+          const float u2 = u * c - v * s, v2 = v * c + u * s;
+          u = u2; v = v2;
+        }
+        vd[2 * i] = a_from_f<E>(u); vd[2 * i + 1] = a_from_f<E>(v);
+      }
+    }
+  }
+}
+
+struct AttnRun {
+  const int32_t* row_ent;
+  const int32_t* ent;
+  const int32_t* page_table;
+  int max_pages, page_size;
+  int H, G, D, V;
+  float scale;
+  int chunk, window;        // 0 = off
+  const float* sink;        // [H] or NULL
+  int ldp, g_off;           // gate column of the packed projection row, g_off < 0: no gate
+  const float* cos_v;       // [positions, V/2] or NULL: turn the output back
+  const float* sin_v;
+};
+
+constexpr int kAttnThreads = 128;
+constexpr int kAttnMaxVPerThread = 4;  // V <= 512
+
+// One CTA per (row, query head).  Keys in tiles of 128: one score per thread, a block-wide running maximum,
+// then the weighted value sum with the threads across the value dimensions (V < 128: several key groups).
+template <typename E>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, const E* __restrict__ vc,
+                   const E* __restrict__ proj, E* __restrict__ out, AttnRun a) {
+  extern __shared__ float sm[];
+  float* q = sm;                      // [D]
+  float* p = q + a.D;                 // [128]
+  float* red = p + kAttnThreads;      // [8]
+  float* ov = red + 8;                // [groups * Vpad]
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int g = h / (a.H / a.G);
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[a.row_ent[row]];
+  const int pos = e.w + (row - e.y);
+  const int32_t* pt = a.page_table + (size_t)e.x * a.max_pages;
+  int lo = 0;
+  if (a.chunk > 0) lo = (pos / a.chunk) * a.chunk;
+  if (a.window > 0 && pos - a.window + 1 > lo) lo = pos - a.window + 1;
+  for (int c = tid; c < a.D; c += kAttnThreads) q[c] = qbuf[((size_t)row * a.H + h) * a.D + c] * a.scale;
+
+  const int groups = a.V >= kAttnThreads ? 1 : kAttnThreads / a.V;
+  const int my_group = a.V >= kAttnThreads ? 0 : tid / a.V;
+  const bool pv_active = my_group < groups;
+  const int d0 = a.V >= kAttnThreads ? tid : tid % a.V;
+  float acc[kAttnMaxVPerThread] = {0.f, 0.f, 0.f, 0.f};
+  float m = a.sink ? a.sink[h] : -INFINITY;  // the sink enters as a term exp(sink - m) = 1 of the denominator
+  float l = a.sink ? 1.f : 0.f;
+  __syncthreads();
+
+  for (int j0 = lo; j0 <= pos; j0 += kAttnThreads) {
+    const int j = j0 + tid;
+    float s = -INFINITY;
+    if (j <= pos) {
+      const E* kr = kc + (((size_t)pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size) * a.D;
+      float d = 0.f;
+      for (int c = 0; c < a.D; ++c) d = fmaf(q[c], a_to_f(kr[c]), d);
+      s = d;
+    }
+    // block maximum
+    float mx = warp_max(s);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float m_new = fmaxf(m, mx);
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    const float w = (j <= pos) ? expf(s - m_new) : 0.f;
+    p[tid] = w;
+    float ws = warp_sum(w);
+    if ((tid & 31) == 0) red[4 + (tid >> 5)] = ws;
+    __syncthreads();
+    l = l * corr + (red[4] + red[5] + red[6] + red[7]);
+    m = m_new;
+    const int cnt = min(kAttnThreads, pos - j0 + 1);
+#pragma unroll
+    for (int i = 0; i < kAttnMaxVPerThread; ++i) acc[i] *= corr;
+    if (pv_active) {
+      for (int jj = my_group; jj < cnt; jj += groups) {
+        const int jk = j0 + jj;
+        const E* vr = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.V;
+        const float wj = p[jj];
+#pragma unroll
+        for (int i = 0; i < kAttnMaxVPerThread; ++i) {
+          const int d = d0 + i * kAttnThreads;
+          if (d < a.V) acc[i] = fmaf(wj, a_to_f(vr[d]), acc[i]);
+        }
+      }
+    }
+  }
+  // sum the key groups, normalise, turn back, gate
+  __syncthreads();
+  if (pv_active) {
+#pragma unroll
+    for (int i = 0; i < kAttnMaxVPerThread; ++i) {
+      const int d = d0 + i * kAttnThreads;
+      if (d < a.V) ov[my_group * a.V + d] = acc[i];
+    }
+  }
+  __syncthreads();
+  float gate = 1.f;
+  if (a.g_off >= 0) gate = 1.f / (1.f + expf(-a_to_f(proj[(size_t)row * a.ldp + a.g_off + h])));
+  const float inv = 1.f / l;
+  E* orow = out + ((size_t)row * a.H + h) * a.V;
+  for (int i = tid; i < a.V / 2; i += kAttnThreads) {
+    float u = 0.f, v = 0.f;
+    for (int gg = 0; gg < groups; ++gg) { u += ov[gg * a.V + 2 * i]; v += ov[gg * a.V + 2 * i + 1]; }
+    u *= inv; v *= inv;
+    if (a.cos_v) {
+      const float c = a.cos_v[(size_t)pos * (a.V / 2) + i], s = a.sin_v[(size_t)pos * (a.V / 2) + i];
+      const float u2 = u * c + v * s, v2 = v * c - u * s;  // by -angle
+      u = u2; v = v2;
+    }
+    orow[2 * i] = a_from_f<E>(u * gate);
+    orow[2 * i + 1] = a_from_f<E>(v * gate);
+  }
+}
+
+}  // namespace dli
+
+using namespace dli;
+
+extern "C" {
+
+int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_cache, const int32_t* row_ent,
+                         const int32_t* ent, const int32_t* page_table, int max_pages, int page_size, int rows, int H,
+                         int G, int D, int V, int rd, int ldp, int q_off, int k_off, int v_off, const float* q_norm,
+                         const float* k_norm, float eps, const float* cos_qk, const float* sin_qk, const float* cos_v,
+                         const float* sin_v, int table_len, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(proj && qbuf && k_cache && v_cache && row_ent && ent && page_table, "dli_attn_prep_append: null pointer");
+  DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0 && D % 2 == 0 && V % 2 == 0 && rd % 2 == 0 && rd <= D,
+                "dli_attn_prep_append: H=%d G=%d D=%d V=%d rd=%d (H %% G == 0, even sizes, rd <= D)", H, G, D, V, rd);
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_attn_prep_append: ent must be 16-byte aligned");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  AttnPrep a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, rd, ldp, q_off, k_off, v_off, q_norm, k_norm,
+             eps, (rd > 0 ? cos_qk : nullptr), sin_qk, cos_v, sin_v, table_len};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<bf16>, dim3(rows), dim3(128), 0, s, (const bf16*)proj, qbuf, (bf16*)k_cache, (bf16*)v_cache, a);
+  else DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<float>, dim3(rows), dim3(128), 0, s, (const float*)proj, qbuf, (float*)k_cache, (float*)v_cache, a);
+  return DLI_OK;
+}
+
+int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
+                    const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
+                    int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
+                    int g_off, const float* cos_v, const float* sin_v, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && row_ent && ent && page_table, "dli_attn_ragged: null pointer");
+  DLI_CHECK_ARG(g_off < 0 || proj, "dli_attn_ragged: a gate needs the projection rows");
+  DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0 && V % 2 == 0 && V <= kAttnThreads * kAttnMaxVPerThread,
+                "dli_attn_ragged: H=%d G=%d D=%d V=%d (H %% G == 0, V even and <= %d)", H, G, D, V,
+                kAttnThreads * kAttnMaxVPerThread);
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v};
+  const int groups = V >= kAttnThreads ? 1 : kAttnThreads / V;
+  const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
+  DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("attn_ragged", attn_ragged_kernel<bf16>, dim3(rows, H), dim3(kAttnThreads), smem, s, qbuf, (const bf16*)k_cache, (const bf16*)v_cache, (const bf16*)proj, (bf16*)out, a);
+  else DLI_LAUNCH("attn_ragged", attn_ragged_kernel<float>, dim3(rows, H), dim3(kAttnThreads), smem, s, qbuf, (const float*)k_cache, (const float*)v_cache, (const float*)proj, (float*)out, a);
+  return DLI_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,285 @@
+// Row-wise pieces of a model whose residual stream is fp32 and whose batch is RAGGED: the rows of one step are
+// portions of different sequences (a prompt's next tokens beside single decoded tokens).  A step is described
+// by two int32 arrays: row_ent[rows] (which entry a row belongs to) and ent[4 * n_ent] = (state slot, first row,
+// number of rows, position of the first row) per entry.
+//
+//   embedding -> fp32 rows, one-number RMS norm, post-norm residual add fused with the next pre-norm,
+//   causal per-channel convolution over time with a per-slot tail state, row gather, a plain tiled GEMM
+//   for element types / shapes the tensor-core GEMM does not take, silu(gate) * up.
+//
+// Element type E of weights and activations: bf16 (dt = 0) or float (dt = 1).  Norms, the convolution and the
+// residual are fp32 for both.
+#include "common.cuh"
+
+namespace dli {
+
+template <typename E> __device__ __forceinline__ float to_f(E v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename E> __device__ __forceinline__ E from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();  // red may still be read from a previous call
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// x[row] = table[ids[row]] as fp32 (the residual stream starts in fp32).
+template <typename E>
+__global__ void __launch_bounds__(128)
+embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ table, float* __restrict__ x, int d, int vocab) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) x[row * d + c] = to_f(table[(size_t)id * d + c]);
+}
+
+// hn = x / sqrt(mean(x^2) + eps) * g  with ONE weight g for the whole row.
+__global__ void __launch_bounds__(256)
+scalar_rmsnorm_kernel(const float* __restrict__ x, float* __restrict__ hn, int d, float eps, float g) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_trigger();
+  const float* xr = x + (size_t)blockIdx.x * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) ss += xr[c] * xr[c];
+  ss = block_sum(ss, red);
+  const float r = g / sqrtf(ss / d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) hn[(size_t)blockIdx.x * d + c] = xr[c] * r;
+}
+
+// x += y / sqrt(mean(y^2) + eps) * g_post; then (hn != NULL) hn = x / sqrt(mean(x^2) + eps) * g_next:
+// the post-norm of one sublayer, the fp32 residual add and the pre-norm of the next sublayer in one pass.
+template <typename E>
+__global__ void __launch_bounds__(256)
+postnorm_add_norm_kernel(const E* __restrict__ y, float* __restrict__ x, float* __restrict__ hn, int d, float eps,
+                         float g_post, float g_next) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_trigger();
+  const size_t o = (size_t)blockIdx.x * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = to_f(y[o + c]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = g_post / sqrtf(ss / d + eps);
+  float s2 = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = x[o + c] + to_f(y[o + c]) * r;
+    x[o + c] = v;
+    s2 += v * v;
+  }
+  if (hn == nullptr) return;
+  s2 = block_sum(s2, red);
+  const float r2 = g_next / sqrtf(s2 / d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) hn[o + c] = x[o + c] * r2;
+}
+
+// out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j]: a causal convolution over time on each channel.  Rows
+// before the entry's first row come from `tail` [slots, taps - 1, d] (the last taps - 1 inputs of the sequence,
+// oldest first); positions before the sequence's start are zero whatever the slot held before.
+template <typename E>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const float* __restrict__ h, const float* __restrict__ tail, const float* __restrict__ w,
+                   const int32_t* __restrict__ row_ent, const int32_t* __restrict__ ent, E* __restrict__ out, int d,
+                   int taps) {
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  const int4 e = reinterpret_cast<const int4*>(ent)[row_ent[row]];  // slot, row0, n, start
+  const int back = row - e.y, pos = e.w + back;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int dist = taps - 1 - j;
+      if (pos - dist < 0) continue;
+      float v;
+      if (dist <= back) v = h[(size_t)(row - dist) * d + c];
+      else v = tail[((size_t)e.x * (taps - 1) + (taps - 1 - (dist - back))) * d + c];
+      acc += w[(size_t)c * taps + j] * v;
+    }
+    out[(size_t)row * d + c] = from_f<E>(h[(size_t)row * d + c] + acc);
+  }
+}
+
+// After the convolution of a step: the tail of every entry's slot becomes the last taps - 1 inputs of the sequence.
+__global__ void __launch_bounds__(256)
+conv_tail_update_kernel(const float* __restrict__ h, float* __restrict__ tail, const int32_t* __restrict__ ent, int d,
+                        int taps) {
+  pdl_wait();
+  pdl_trigger();
+  const int4 e = reinterpret_cast<const int4*>(ent)[blockIdx.x];
+  const int keep = taps - 1, end = e.w + e.z;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float* t = tail + (size_t)e.x * keep * d + c;
+    for (int i = 0; i < keep; ++i) {  // ascending: slot i reads old slot i + n (n >= 1), never one already written
+      const int p = end - keep + i;
+      float v = 0.f;
+      if (p >= e.w) v = h[(size_t)(e.y + p - e.w) * d + c];
+      else if (p >= 0) v = t[(size_t)(keep - (e.w - p)) * d];
+      t[(size_t)i * d] = v;
+    }
+  }
+}
+
+// out[i] = E(src[rows[i]])
+template <typename E>
+__global__ void __launch_bounds__(256)
+gather_cast_kernel(const float* __restrict__ src, const int32_t* __restrict__ rows, E* __restrict__ out, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t r = rows[blockIdx.x];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) out[(size_t)blockIdx.x * d + c] = from_f<E>(src[r * d + c]);
+}
+
+// y[M,N] = x[M,K] . w[N,K]^T, fp32 accumulation on the CUDA cores (true fp32 for float operands).  64x64 tile,
+// 16 deep, 4x4 outputs per thread.  Any M, N, K; rows of x and y may be strided.
+template <typename E, typename O>
+__global__ void __launch_bounds__(256)
+linear_any_kernel(const E* __restrict__ x, const E* __restrict__ w, O* __restrict__ y, int M, int N, int K, int ldx,
+                  int ldy) {
+  __shared__ float xs[16][64 + 4];
+  __shared__ float ws[16][64 + 4];
+  pdl_wait();
+  pdl_trigger();
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i >> 4, k = i & 15;
+      xs[k][r] = (m0 + r < M && k0 + k < K) ? to_f(x[(size_t)(m0 + r) * ldx + k0 + k]) : 0.f;
+      ws[k][r] = (n0 + r < N && k0 + k < K) ? to_f(w[(size_t)(n0 + r) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < M && n < N) y[(size_t)m * ldy + n] = from_f<O>(acc[i][j]);
+    }
+}
+
+// act[m, f] = silu(gu[m, f]) * gu[m, F + f]
+template <typename E>
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const E* __restrict__ gu, E* __restrict__ act, int F, int ld) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t m = blockIdx.x;
+  for (int f = threadIdx.x; f < F; f += blockDim.x) {
+    const float g = to_f(gu[m * ld + f]), u = to_f(gu[m * ld + F + f]);
+    act[m * F + f] = from_f<E>(to_f(from_f<E>(silu_f(g))) * u);
+  }
+}
+
+}  // namespace dli
+
+using namespace dli;
+
+#define DT_CHECK(dt) DLI_CHECK_ARG((dt) == 0 || (dt) == 1, "element type %d: 0 = bf16, 1 = float", dt)
+
+extern "C" {
+
+int dli_embedding_f32(const int32_t* ids, const void* table, float* x, int rows, int d, int vocab, int dt,
+                      dli_stream_t stream) {
+  DLI_CHECK_ARG(ids && table && x && d > 0 && vocab > 0, "dli_embedding_f32: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(128), 0, s, ids, (const bf16*)table, x, d, vocab);
+  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(128), 0, s, ids, (const float*)table, x, d, vocab);
+  return DLI_OK;
+}
+
+int dli_scalar_rmsnorm_f32(const float* x, float* hn, int rows, int d, float eps, float g, dli_stream_t stream) {
+  DLI_CHECK_ARG(x && hn && d > 0, "dli_scalar_rmsnorm_f32: null pointer or empty shape");
+  if (rows <= 0) return DLI_OK;
+  DLI_LAUNCH("scalar_rmsnorm", scalar_rmsnorm_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), x, hn, d, eps, g);
+  return DLI_OK;
+}
+
+int dli_postnorm_add_norm(const void* y, float* x, float* hn, int rows, int d, float eps, float g_post, float g_next,
+                          int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(y && x && d > 0, "dli_postnorm_add_norm: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("postnorm_add_norm", postnorm_add_norm_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)y, x, hn, d, eps, g_post, g_next);
+  else DLI_LAUNCH("postnorm_add_norm", postnorm_add_norm_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)y, x, hn, d, eps, g_post, g_next);
+  return DLI_OK;
+}
+
+int dli_causal_conv_ragged(const float* h, float* tail, const float* w, const int32_t* row_ent, const int32_t* ent,
+                           void* out, int rows, int n_ent, int d, int taps, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(h && w && row_ent && ent && out && d > 0 && taps >= 1, "dli_causal_conv_ragged: null pointer or empty shape");
+  DLI_CHECK_ARG(tail || taps == 1, "dli_causal_conv_ragged: taps > 1 needs a tail state");
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_causal_conv_ragged: ent must be 16-byte aligned");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("causal_conv", causal_conv_kernel<bf16>, dim3(rows), dim3(256), 0, s, h, (const float*)tail, w, row_ent, ent, (bf16*)out, d, taps);
+  else DLI_LAUNCH("causal_conv", causal_conv_kernel<float>, dim3(rows), dim3(256), 0, s, h, (const float*)tail, w, row_ent, ent, (float*)out, d, taps);
+  if (taps > 1) DLI_LAUNCH("conv_tail_update", conv_tail_update_kernel, dim3(n_ent), dim3(256), 0, s, h, tail, ent, d, taps);
+  return DLI_OK;
+}
+
+int dli_gather_cast(const float* src, const int32_t* rows, void* out, int n, int d, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(src && rows && out && d > 0, "dli_gather_cast: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (n <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("gather_cast", gather_cast_kernel<bf16>, dim3(n), dim3(256), 0, s, src, rows, (bf16*)out, d);
+  else DLI_LAUNCH("gather_cast", gather_cast_kernel<float>, dim3(n), dim3(256), 0, s, src, rows, (float*)out, d);
+  return DLI_OK;
+}
+
+int dli_linear_any(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldy, int dt,
+                   dli_stream_t stream) {
+  DLI_CHECK_ARG(x && w && y && N > 0 && K > 0 && ldx >= K && ldy >= N, "dli_linear_any: null pointer or bad shape");
+  DT_CHECK(dt);
+  if (M <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid((N + 63) / 64, (M + 63) / 64);
+  if (dt == 0) DLI_LAUNCH("linear_any", linear_any_kernel<bf16, bf16>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, ldx, ldy);
+  else DLI_LAUNCH("linear_any", linear_any_kernel<float, float>, grid, dim3(256), 0, s, (const float*)x, (const float*)w, (float*)y, M, N, K, ldx, ldy);
+  return DLI_OK;
+}
+
+int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(gu && act && F > 0 && ld >= 2 * F, "dli_silu_mul: null pointer or bad shape");
+  DT_CHECK(dt);
+  if (M <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("silu_mul", silu_mul_kernel<bf16>, dim3(M), dim3(256), 0, s, (const bf16*)gu, (bf16*)act, F, ld);
+  else DLI_LAUNCH("silu_mul", silu_mul_kernel<float>, dim3(M), dim3(256), 0, s, (const float*)gu, (float*)act, F, ld);
+  return DLI_OK;
+}
+
+}  // extern "C"

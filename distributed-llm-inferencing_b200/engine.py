@@ -157,16 +157,20 @@ class PagedKVCache:
     layers.  Replaces the grow-by-torch.cat cache of TF:cache_utils.py:102-121
     (an O(S) copy per layer per token) with in-place page writes."""
 
-    def __init__(self, n_layers, n_kv, hd, page_size, max_seqs, max_seq_len, device, pool_tokens=None):
+    def __init__(self, n_layers, n_kv, hd, page_size, max_seqs, max_seq_len, device, pool_tokens=None,
+                 layer_shapes=None, dtype=BF):
         """pool_tokens: size of the page pool in tokens; default max_seqs * max_seq_len (every sequence can reach the
         maximum at once).  A smaller pool is shared on demand: sequences reserve pages as they grow (the continuous
-        batcher does) and a reservation that finds the pool empty raises."""
+        batcher does) and a reservation that finds the pool empty raises.
+        layer_shapes: [(kv heads, key size, value size)] per layer for models whose layers differ (or whose keys and
+        values differ in size); default n_layers x (n_kv, hd, hd).  dtype: element type of the pools."""
         self.page_size = page_size
         self.max_pages = (max_seq_len + page_size - 1) // page_size
         self.num_pages = max_seqs * self.max_pages if not pool_tokens else \
             max(self.max_pages, (int(pool_tokens) + page_size - 1) // page_size)
-        self.k = [torch.zeros(self.num_pages, n_kv, page_size, hd, dtype=BF, device=device) for _ in range(n_layers)]
-        self.v = [torch.zeros(self.num_pages, n_kv, page_size, hd, dtype=BF, device=device) for _ in range(n_layers)]
+        shapes = layer_shapes if layer_shapes is not None else [(n_kv, hd, hd)] * n_layers
+        self.k = [torch.zeros(self.num_pages, g, page_size, dk, dtype=dtype, device=device) for g, dk, _ in shapes]
+        self.v = [torch.zeros(self.num_pages, g, page_size, dv, dtype=dtype, device=device) for g, _, dv in shapes]
         self.free: List[int] = list(range(self.num_pages - 1, -1, -1))
         self.owned: Dict[int, List[int]] = {}
         self._host_table = torch.zeros(max_seqs, self.max_pages, dtype=torch.int32)
@@ -207,7 +211,7 @@ class PagedKVCache:
             self.release(s)
 
     def bytes(self) -> int:
-        return sum(t.numel() * 2 for t in self.k) * 2
+        return sum(t.numel() * t.element_size() for t in self.k + self.v)
 
 
 class ShardEngine:

@@ -438,3 +438,117 @@ def linear_argmax(h, w, logits, scratch, tokens=None, cand=None, ln_w=None, eps=
         _bytes(scratch), _stream()))
     launch_count += 2
     return tokens if tokens is not None else cand
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Ragged steps with an fp32 residual stream (ragged_rows.cu, attn_ragged.cu, mlstm.cu).  `dt` (0 = bf16, 1 = float)
+# is the element type of weights, activations and caches; the wrappers take it from the tensors.
+def _dt(t) -> int:
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise ValueError(f"element type {t.dtype}: bf16 or float32")
+
+
+def _call(name, n_launch, *args):
+    global launch_count
+    _lib.check(name, getattr(_lib.load(), name)(*args))
+    launch_count += n_launch
+
+
+def _f32(*ts):
+    for t in ts:
+        _req(t, torch.float32)
+
+
+def _i32(*ts):
+    for t in ts:
+        _req(t, torch.int32)
+
+
+def embedding_f32(ids, table, out):
+    """ids int32 [rows]; table [V, d] bf16 / float -> out float32 [rows, d]."""
+    _i32(ids), _req(table, table.dtype), _f32(out)
+    _call("dli_embedding_f32", 1, _p(ids), _p(table), _p(out), ids.numel(), table.shape[1], table.shape[0], _dt(table),
+          _stream())
+    return out
+
+
+def scalar_rmsnorm(x, g: float, eps: float, out):
+    """out = x / sqrt(mean(x^2) + eps) * g (one weight per norm); x, out float32 [rows, d]."""
+    _f32(x, out)
+    _call("dli_scalar_rmsnorm_f32", 1, _p(x), _p(out), x.shape[0], x.shape[1], float(eps), float(g), _stream())
+    return out
+
+
+def postnorm_add_norm(y, x, g_post: float, eps: float, hn=None, g_next: float = 1.0):
+    """x += y / rms(y) * g_post (x float32, in place); hn = x / rms(x) * g_next when hn is given."""
+    _req(y, y.dtype), _f32(x, hn)
+    _call("dli_postnorm_add_norm", 1, _p(y), _p(x), _p(hn), x.shape[0], x.shape[1], float(eps), float(g_post),
+          float(g_next), _dt(y), _stream())
+    return x
+
+
+def causal_conv_ragged(h, tail, w, row_ent, ent, out):
+    """out = h + conv(h) over time per channel (w float32 [d, taps]); tail float32 [slots, taps-1, d] is advanced."""
+    _f32(h, tail, w), _i32(row_ent, ent), _req(out, out.dtype)
+    taps = w.shape[1]
+    _call("dli_causal_conv_ragged", 2 if taps > 1 else 1, _p(h), _p(tail), _p(w), _p(row_ent), _p(ent), _p(out),
+          h.shape[0], ent.numel() // 4, h.shape[1], taps, _dt(out), _stream())
+    return out
+
+
+def gather_cast(src, rows, out):
+    """out[i] = src[rows[i]] cast to out's element type; src float32 [n, d]."""
+    _f32(src), _i32(rows), _req(out, out.dtype)
+    _call("dli_gather_cast", 1, _p(src), _p(rows), _p(out), rows.numel(), src.shape[1], _dt(out), _stream())
+    return out
+
+
+def linear_any(x, w, out):
+    """out = x @ w.T on the CUDA cores (fp32 accumulation; true fp32 for float operands).  Any shape; x and out
+    may be row-strided views."""
+    if x.dtype != w.dtype or out.dtype != w.dtype or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
+        raise ValueError("linear_any: one element type, unit inner strides")
+    M, K = x.shape
+    _call("dli_linear_any", 1, _p(x), _p(w), _p(out), M, w.shape[0], K, x.stride(0), out.stride(0), _dt(w), _stream())
+    return out
+
+
+def silu_mul(gu, out):
+    """out[m, f] = silu(gu[m, f]) * gu[m, F + f]."""
+    _req(gu, gu.dtype), _req(out, gu.dtype)
+    _call("dli_silu_mul", 1, _p(gu), _p(out), gu.shape[0], out.shape[1], gu.shape[1], _dt(gu), _stream())
+    return out
+
+
+def attn_prep_append(proj, qbuf, k_cache, v_cache, row_ent, ent, page_table, H, G, D, V, rd, q_off, k_off, v_off,
+                     q_norm, k_norm, eps, cos_qk, sin_qk, cos_v, sin_v):
+    """q/k head norms, rotation and value rotation of a ragged step; q -> qbuf (float32), k / v -> the paged caches."""
+    _req(proj, proj.dtype), _req(k_cache, proj.dtype), _req(v_cache, proj.dtype)
+    _f32(qbuf, q_norm, k_norm, cos_qk, sin_qk, cos_v, sin_v), _i32(row_ent, ent, page_table)
+    tl = cos_qk.shape[0] if cos_qk is not None else (cos_v.shape[0] if cos_v is not None else 0)
+    _call("dli_attn_prep_append", 1, _p(proj), _p(qbuf), _p(k_cache), _p(v_cache), _p(row_ent), _p(ent), _p(page_table),
+          page_table.shape[1], k_cache.shape[2], proj.shape[0], H, G, D, V, rd, proj.shape[1], q_off, k_off, v_off,
+          _p(q_norm), _p(k_norm), float(eps), _p(cos_qk), _p(sin_qk), _p(cos_v), _p(sin_v), tl, _dt(proj), _stream())
+
+
+def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, G, D, V, scale, chunk=0, window=0,
+                sink=None, g_off=-1, cos_v=None, sin_v=None):
+    """Chunk- / window-masked attention with an optional sink and output gate over the paged cache -> out [rows, H*V]."""
+    _f32(qbuf, sink, cos_v, sin_v), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
+    _call("dli_attn_ragged", 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(row_ent), _p(ent),
+          _p(page_table), page_table.shape[1], k_cache.shape[2], qbuf.shape[0], H, G, D, V, float(scale), int(chunk),
+          int(window), _p(sink), proj.shape[1], g_off, _p(cos_v), _p(sin_v), _dt(k_cache), _stream())
+    return out
+
+
+def mlstm_ragged(proj, o_scratch, out, ent, H, D, V, q_off, k_off, v_off, i_off, f_off, g_off, i_bias, f_bias, cap,
+                 out_w, eps, S, n, m):
+    """Matrix-memory recurrence over the rows of every entry + head norm, weight and output gate -> out [rows, H*V]."""
+    _req(proj, proj.dtype), _req(out, proj.dtype), _f32(o_scratch, i_bias, f_bias, out_w, S, n, m), _i32(ent)
+    _call("dli_mlstm_ragged", 2, _p(proj), _p(o_scratch), _p(out), _p(ent), ent.numel() // 4, proj.shape[0], H, D, V,
+          proj.shape[1], q_off, k_off, v_off, i_off, f_off, g_off, _p(i_bias), _p(f_bias), float(cap), _p(out_w),
+          float(eps), _p(S), _p(n), _p(m), _dt(proj), _stream())
+    return out

@@ -390,6 +390,60 @@ int dli_decode_advance(const int32_t* tokens, int32_t* token_log, int32_t* posit
                        int32_t* seq_lens, int32_t* step, int B, int log_capacity,
                        dli_stream_t stream);
 
+/* ---- ragged steps with an fp32 residual stream ---------------------------------
+ * Models whose layers differ in kind (attention with per-head norms, partial
+ * interleaved rotation, rotated values, chunk mask, sink and gate; matrix-memory
+ * recurrent layers; short causal convolutions in front of every sublayer) run on
+ * a RAGGED batch: the rows of a step are the next tokens of several sequences, a
+ * prompt's portion beside single decoded tokens.  row_ent[rows] names the entry
+ * of a row, ent[4 * n_ent] = (state slot, first row, rows, first position) per
+ * entry (16-byte aligned).  `dt` is the element type of weights, activations and
+ * caches: 0 = bf16, 1 = float (true fp32 arithmetic).  The residual stream x,
+ * every norm, convolution state, recurrent state, angle, score and softmax weight
+ * is fp32 for both. */
+int dli_embedding_f32(const int32_t* ids, const void* table, float* x, int rows, int d, int vocab, int dt,
+                      dli_stream_t stream);
+/* hn = x / sqrt(mean(x^2) + eps) * g, one weight g per norm. */
+int dli_scalar_rmsnorm_f32(const float* x, float* hn, int rows, int d, float eps, float g, dli_stream_t stream);
+/* x += y / rms(y) * g_post; hn = x / rms(x) * g_next (hn may be NULL). */
+int dli_postnorm_add_norm(const void* y, float* x, float* hn, int rows, int d, float eps, float g_post, float g_next,
+                          int dt, dli_stream_t stream);
+/* out = h + conv(h): causal per-channel convolution over time, w [d, taps] fp32 (tap taps-1 is the current row);
+ * tail [slots, taps-1, d] fp32 holds each sequence's last inputs and is advanced by the call. */
+int dli_causal_conv_ragged(const float* h, float* tail, const float* w, const int32_t* row_ent, const int32_t* ent,
+                           void* out, int rows, int n_ent, int d, int taps, int dt, dli_stream_t stream);
+int dli_gather_cast(const float* src, const int32_t* rows, void* out, int n, int d, int dt, dli_stream_t stream);
+/* y[M,N] = x[M,K] . w[N,K]^T on the CUDA cores with fp32 accumulation: any shape, both element types. */
+int dli_linear_any(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldy, int dt,
+                   dli_stream_t stream);
+/* act[m, f] = silu(gu[m, f]) * gu[m, F + f] */
+int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_stream_t stream);
+
+/* Attention of a ragged step.  dli_attn_prep_append: per-head RMS norm of q and k (q_norm / k_norm [D] fp32 or NULL),
+ * rotation of the first rd dims (interleaved pairs; cos_qk / sin_qk [table_len, rd/2] fp32), rotation of the values
+ * over all V dims (cos_v / sin_v [table_len, V/2] or NULL), q -> qbuf [rows, H, D] fp32, k and v -> the paged caches
+ * [pages, G, page_size, D] / [pages, G, page_size, V].  dli_attn_ragged: scores (q . k) * scale over the keys the
+ * chunk mask (chunk > 0: same block of `chunk` positions) and the window (window > 0) leave, softmax with an optional
+ * sink term exp(sink[h]) in the denominator, output turned back by the row's position (cos_v / sin_v) and multiplied
+ * by sigmoid(proj[row, g_off + h]) (g_off < 0: no gate) -> out [rows, H, V]. */
+int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_cache, const int32_t* row_ent,
+                         const int32_t* ent, const int32_t* page_table, int max_pages, int page_size, int rows, int H,
+                         int G, int D, int V, int rd, int ldp, int q_off, int k_off, int v_off, const float* q_norm,
+                         const float* k_norm, float eps, const float* cos_qk, const float* sin_qk, const float* cos_v,
+                         const float* sin_v, int table_len, int dt, dli_stream_t stream);
+int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
+                    const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
+                    int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
+                    int g_off, const float* cos_v, const float* sin_v, int dt, dli_stream_t stream);
+
+/* Matrix-memory recurrent layer (mLSTM, stabilised): q, k, v, gate pre-activations and the output gate are columns
+ * of proj [rows, ldp]; state S [slots, H, D, V], n [slots, H, D], m [slots, H] fp32 is read and advanced (an entry
+ * at position 0 starts from zero); o_scratch [rows, H, V] fp32; y [rows, H*V] = o / rms_head(o) * out_w * sigmoid(g). */
+int dli_mlstm_ragged(const void* proj, float* o_scratch, void* y, const int32_t* ent, int n_ent, int rows, int H, int D,
+                     int V, int ldp, int q_off, int k_off, int v_off, int i_off, int f_off, int g_off,
+                     const float* i_bias, const float* f_bias, float cap, const float* out_w, float eps, float* S,
+                     float* n, float* m, int dt, dli_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
