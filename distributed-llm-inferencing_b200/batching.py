@@ -203,3 +203,144 @@ class ContinuousBatcher:
         self._stop.set()
         if self._thread:
             self._thread.join(timeout=10)
+
+
+class RaggedBatcher:
+    """Scheduler for engines with a ragged step function (ragged_engine.RaggedEngine): chunked prefill beside decode.
+
+    Where ContinuousBatcher prefills each request alone and only decodes together, every step here is ONE batch of
+    whatever the live requests need next: up to `chunk` tokens of a prompt that is not through yet (the budget of
+    `chunk` prompt tokens per step is shared, so decoding rows never wait for a whole long prompt), or the single
+    token a decoding request produced in the previous step.  A request is admitted when a state slot is free and
+    leaves it — pages and slot — when it is done.  The token at position p of a sampling request is drawn with the
+    key (seed, p - 1), whichever step and row computed it; greedy requests take the argmax."""
+
+    def __init__(self, engine, max_live: Optional[int] = None, chunk: int = 512, temperature: float = 0.8,
+                 top_k: int = 50, top_p: float = 0.95):
+        if not hasattr(engine, "step"):
+            raise ValueError("RaggedBatcher needs an engine with a ragged step function")
+        self.eng = engine
+        self.max_live = min(max_live or engine.max_batch, engine.max_batch)
+        self.chunk = int(chunk)
+        self.pending: "queue.Queue[_Request]" = queue.Queue()
+        self.live: List[tuple] = []   # (request, slot)
+        self._params = dict(temperature=float(temperature), top_k=int(top_k), top_p=float(top_p))
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self.steps = 0
+
+    def submit(self, input_ids, max_length: int = 100, timeout: Optional[float] = None, do_sample: bool = False,
+               seed: int = 0) -> Future:
+        ids = torch.as_tensor(input_ids, dtype=torch.int64).reshape(-1).cpu()
+        req = _Request(ids, int(max_length), None if timeout is None else time.time() + timeout,
+                       do_sample=bool(do_sample), seed=int(seed))
+        req.future.request = req
+        req.fed = 0  # prompt tokens that went through the engine
+        if len(ids) == 0:
+            req.future.set_exception(ValueError("empty prompt"))
+        elif req.max_length > self.eng.max_seq_len:
+            req.future.set_exception(ValueError(f"max_length {req.max_length} > engine max_seq_len {self.eng.max_seq_len}"))
+        elif req.max_length <= len(ids):
+            try:
+                check_max_length(len(ids), req.max_length)
+            except ValueError as e:
+                req.future.set_exception(e)
+        else:
+            self.pending.put(req)
+        return req.future
+
+    def plan(self) -> List[tuple]:
+        """[(request, slot, tokens, produces)] of the next step: decoding requests bring their last token; prompts
+        share a budget of `chunk` tokens, oldest first.  produces: the step yields the request's next token."""
+        plan, budget = [], self.chunk
+        for req, slot in self.live:
+            if req.fed >= len(req.ids):
+                plan.append((req, slot, [req.out[-1]], True))
+        for req, slot in self.live:
+            left = len(req.ids) - req.fed
+            if left > 0 and budget > 0:
+                n = min(left, budget)
+                budget -= n
+                plan.append((req, slot, req.ids[req.fed:req.fed + n].tolist(), n == left))
+        return plan
+
+    def _retire(self, req, slot, error: Optional[Exception] = None) -> None:
+        self.live = [(r, s) for r, s in self.live if r is not req]
+        self.eng.close_sequence(slot)
+        if error is not None:
+            req.future.set_exception(error)
+        else:
+            req.future.set_result(torch.cat((req.ids, torch.tensor(req.out, dtype=torch.int64))))
+
+    def step(self) -> int:
+        """Admit what fits, run one ragged step, hand every produced token to its request.  Returns the number of
+        live requests after the step."""
+        eng = self.eng
+        while len(self.live) < self.max_live:
+            try:
+                req = self.pending.get_nowait()
+            except queue.Empty:
+                break
+            self.live.append((req, eng.open_sequence()))
+        for req, slot in list(self.live):
+            if req.deadline is not None and time.time() > req.deadline:
+                self._retire(req, slot, TimeoutError("Inference generation timed out"))
+        plan = self.plan()
+        if not plan:
+            return len(self.live)
+        try:
+            logits = eng.step([(slot, toks) for _, slot, toks, _ in plan],
+                              [[len(toks) - 1] if prod else [] for _, _, toks, prod in plan])
+        except RuntimeError as e:  # the page pool is empty: the youngest request waits for pages, or fails alone
+            req, slot = self.live[-1]
+            if len(self.live) > 1 and not req.out:
+                self.live.pop()
+                eng.close_sequence(slot)
+                req.fed = 0
+                self.pending.put(req)
+            else:
+                self._retire(req, slot, e)
+            return len(self.live)
+        producers = [(req, slot, toks) for req, slot, toks, prod in plan if prod]
+        for req, _, toks, _ in plan:
+            if req.fed < len(req.ids):
+                req.fed += len(toks)
+        if producers:
+            if logits.dtype != torch.bfloat16:
+                logits = logits.to(torch.bfloat16)
+            from . import ops
+            toks_dev = ops.argmax(logits)
+            if any(r.do_sample for r, _, _ in producers):
+                dev = logits.device
+                seeds = torch.tensor([r.seed for r, _, _ in producers], dtype=torch.int64, device=dev)
+                # position of the token that produced the logits
+                steps = torch.tensor([len(r.ids) + len(r.out) - 1 for r, _, _ in producers], dtype=torch.int32, device=dev)
+                mask = torch.tensor([int(r.do_sample) for r, _, _ in producers], dtype=torch.int32, device=dev)
+                ops.sample_rows(logits, toks_dev, seeds, steps, mask, **self._params)
+            host = toks_dev.cpu().tolist()
+            for (req, slot, _), t in zip(producers, host):
+                req.out.append(int(t))
+                if len(req.ids) + len(req.out) >= req.max_length or req.out[-1] in eng.eos_token_ids:
+                    self._retire(req, slot)
+        self.steps += 1
+        return len(self.live)
+
+    def serve_forever(self, idle_sleep: float = 0.001) -> None:
+        torch.cuda.set_device(self.eng.device)
+        while not self._stop.is_set():
+            try:
+                if self.step() == 0 and self.pending.empty():
+                    time.sleep(idle_sleep)
+            except Exception as e:  # noqa: BLE001 — fail the requests in flight, keep serving
+                for req, slot in list(self.live):
+                    self._retire(req, slot, e)
+
+    def start(self) -> "RaggedBatcher":
+        self._thread = threading.Thread(target=self.serve_forever, daemon=True)
+        self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=10)

@@ -132,6 +132,16 @@ class Worker:
         if self.device != "cuda":
             raise RuntimeError("this worker has no CPU path: it needs a CUDA device and USE_GPU=1")
         cfg = json.load(open(os.path.join(path, "config.json")))
+        from . import models
+        if models.family(cfg) != "uniform":
+            # layer-by-layer designs (models.py) run on the ragged engine, whole on one GPU
+            if start != 0 or end is not None or head_shard is not None:
+                raise ValueError("this model family is served unsharded")
+            eng = models.load_engine(path, device=self.cuda_device, max_seq_len=self.max_seq_len,
+                                     max_batch=max_batch or max(self.max_batch, 1), kv_pool_tokens=self.kv_pool_tokens)
+            eng.eos_token_ids, eng.pad_token_id = _stop_tokens(path, cfg)
+            eng.prefill_chunk = self.prefill_chunk
+            return eng
         spec = ModelSpec.from_hf_config(cfg)
         if max_batch is None:
             max_batch = self.max_batch if end is None else 1
@@ -175,9 +185,11 @@ class Worker:
                 self.loaded_tokenizers[model_name] = _load_tokenizer(path)
             self.loaded_models[model_name] = self._engine(path)
             if self.batching:
-                from .batching import ContinuousBatcher
+                from .batching import ContinuousBatcher, RaggedBatcher
 
-                self.batchers[model_name] = ContinuousBatcher(self.loaded_models[model_name]).start()
+                eng = self.loaded_models[model_name]
+                self.batchers[model_name] = (RaggedBatcher(eng, chunk=self.prefill_chunk or 512) if hasattr(eng, "step")
+                                             else ContinuousBatcher(eng)).start()
             return {"status": "success", "message": f"Model {model_name} loaded successfully on {self.device}"}, 200
         except Exception as e:  # noqa: BLE001 — the reference maps every failure to 500
             return {"status": "error", "message": f"Failed to load model: {str(e)}"}, 500
