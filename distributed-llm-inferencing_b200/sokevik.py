@@ -78,7 +78,7 @@ def random_state_dict(spec: HybridSpec, seed: int = 0, std: float = 0.05, device
     W = spec.width
 
     def n(*shape, s=std, mean=0.0):
-        return (mean + s * torch.randn(*shape, generator=g)).to(torch.bfloat16).to(device)
+        return (mean + s * torch.randn(tuple(shape), generator=g)).to(torch.bfloat16).to(device)
 
     sd = {"embed": n(spec.vocab, W, s=1.0), "head": n(spec.vocab, W), "final.norm": n(mean=1.0, s=0.1)}
     for i, L in enumerate(spec.layers):

@@ -165,7 +165,7 @@ def test_attention_one_key_stands_out(cuts, target):
     torch.manual_seed(4)
     chunk, page = 128, 16
     # one rotated pair (dims 0, 1); the direction that carries the signal (3) is outside it.  The head norm (unit
-    # weights) brings every q and k to unit RMS, so the marked pair scores 8 * scale and the others about +-3 * scale.
+    # weights) brings every q and k to unit RMS: the marked pair scores 8 * scale, every other key exactly 0.
     m = {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 4.0, "mask": {"size": chunk},
          "rot": {"base": 50.0, "dims": 2}}
     T = 260
@@ -173,6 +173,7 @@ def test_attention_one_key_stands_out(cuts, target):
     j = {"first_in_chunk": 128, "last_of_previous_chunk": 127, "page_border": 143, "far_in_chunk": 129}[target]
     q, k = torch.randn(T, 16), torch.randn(T, 8)
     v, g = torch.randn(T, 8), torch.zeros(T, 2)
+    k[:, 3] = 0
     q[i, :8] = 0
     q[i, 3] = 1.0                              # head 0 of position i asks for direction 3 ...
     k[j] = 0
