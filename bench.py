@@ -392,6 +392,185 @@ def run_reference(args, spec):
 
 
 # ---------------------------------------------------------------------------------- main
+# ---------------------------------------------------------------------------------- layer-by-layer family
+HYBRID_SIZES = {
+    # name: (width, heads, kv heads, head size, feed-forward, layers, vocab)
+    "1b": (2048, 16, 4, 128, 8192, 4, 32000),
+    "8b": (4096, 32, 8, 128, 14336, 4, 32000),
+}
+
+
+def hybrid_config(width, heads, kv, hd, ff, layers, vocab, chunk):
+    """Layers alternate attention and mLSTM mixers, every one with a feed-forward: the Sokevik design at the sizes of
+    a Llama layer (same width, heads, head size and feed-forward size as the uniform stack it is compared with)."""
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": chunk},
+                     "rot": {"base": 500000.0, "dims": hd, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    rec = {"type": "mlstm", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads // 2, "dim": hd, "vdim": 2 * hd, "gate_cap": 15.0}}
+    return {"architecture": "Sokevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "layers": [att if i % 2 == 0 else rec for i in range(layers)]}
+
+
+def run_hybrid_compare(args, peaks):
+    """Prefill and decode throughput of the layer-by-layer family (RaggedEngine) beside the uniform Llama stack
+    (ShardEngine) at equal layer sizes, random weights, plus the time of each kind of kernel per step (CUDA events
+    around eager steps).  One JSON line; the default workload of this file is untouched."""
+    from dli_b200 import ops, sokevik
+    from dli_b200.engine import ModelSpec, ShardEngine
+    from dli_b200.ragged_engine import RaggedEngine
+
+    T, K, W = args.ctx, args.steps, args.warmup
+    out = {"metric": "hybrid_vs_uniform", "unit": "tokens/s", "ctx": T, "steps": K, "warmup": W, "dtype": "bf16",
+           "data": "synthetic", "peaks": peaks, "sizes": {}}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > L2: written between timed prefills
+    for name in args.hybrid_sizes.split(","):
+        width, heads, kv, hd, ff, layers, vocab = HYBRID_SIZES[name]
+        res = {}
+        # ---- the new family
+        cfg = hybrid_config(width, heads, kv, hd, ff, layers, vocab, chunk=T)
+        spec = sokevik.spec_from_config(cfg)
+        eng = RaggedEngine(spec, max_batch=max(args.batch, 8), max_seq_len=T + K + W + 64, page_size=args.page_size)
+        eng.load_tensors(sokevik.model_tensors(spec, sokevik.random_state_dict(spec, seed=1, std=0.02, device="cuda")))
+        g = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, vocab, (T,), generator=g).tolist()
+
+        def prefill_once():
+            s = eng.open_sequence()
+            eng.step([(s, prompt)])
+            return s
+
+        for _ in range(2):
+            eng.close_sequence(prefill_once())
+        times = []
+        for _ in range(3):
+            flush.fill_(1)
+            slot = [None]
+            times.append(ev_time_ms(lambda: slot.__setitem__(0, prefill_once())))
+            eng.close_sequence(slot[0])
+        res["hybrid_prefill_tok_s"] = round(T / (statistics.median(times) / 1e3), 1)
+        for B in sorted({1, args.batch if args.batch > 1 else 8}):
+            slots = []
+            for b in range(B):
+                slots.append(prefill_once())
+            step = lambda: eng.step([(s, [7]) for s in slots])  # noqa: E731
+            for _ in range(W):
+                step()
+            n0 = ops.launch_count
+            ms = ev_time_ms(lambda: [step() for _ in range(K)])
+            res[f"hybrid_decode_b{B}_tok_s"] = round(B * K / (ms / 1e3), 1)
+            res[f"hybrid_decode_b{B}_launches_per_step"] = (ops.launch_count - n0) // K
+            for s in slots:
+                eng.close_sequence(s)
+        res["hybrid_weight_gb"] = round(eng.weight_bytes() / 1e9, 3)
+        res["kernels"] = hybrid_kernel_times(eng, spec, T, peaks)
+        eng.unload()
+        del eng
+        torch.cuda.empty_cache()
+        # ---- the uniform stack at the same sizes
+        lspec = ModelSpec("llama", layers, width, heads, kv, hd, ff, vocab, 1e-6, 500000.0, 0, T + K + W + 64)
+        le = ShardEngine(lspec, max_batch=max(args.batch, 8), max_seq_len=T + K + W + 64, page_size=args.page_size)
+        le.load_random(seed=1)
+        ids = torch.tensor(prompt, dtype=torch.int32, device="cuda")
+        le.start_batch(1, T, T + K + W + 8)
+        for _ in range(2):
+            le.prefill(1, T, ids=ids)
+        times = []
+        for _ in range(3):
+            flush.fill_(1)
+            times.append(ev_time_ms(lambda: le.prefill(1, T, ids=ids)))
+        res["uniform_prefill_tok_s"] = round(T / (statistics.median(times) / 1e3), 1)
+        for B in sorted({1, args.batch if args.batch > 1 else 8}):
+            le.start_batch(B, T, T + K + W + 8)
+            le.prefill(B, T, ids=ids.repeat(B))
+            for _ in range(W):
+                le.decode_step(B)
+            ms = ev_time_ms(lambda: [le.decode_step(B) for _ in range(K)])
+            res[f"uniform_decode_b{B}_tok_s"] = round(B * K / (ms / 1e3), 1)
+        res["uniform_weight_gb"] = round(le.weight_bytes() / 1e9, 3)
+        le.unload()
+        del le
+        torch.cuda.empty_cache()
+        out["sizes"][name] = res
+    return out
+
+
+def hybrid_kernel_times(eng, spec, T, peaks):
+    """Each kernel of the ragged path alone at the step sizes of the comparison: a T-token portion (prefill) and one
+    token after T (decode), against its algorithmic HBM bytes (or FLOPs) and the measured peaks."""
+    from dli_b200 import ops
+
+    dev, E = eng.device, eng.dtype
+    W = spec.width
+    att = next(L.mixer for L in spec.layers if L.mixer.kind == "attention")
+    rec = next(L.mixer for L in spec.layers if L.mixer.kind == "mlstm")
+    li_a = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "attention")
+    li_r = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "mlstm")
+    slot = eng.open_sequence()
+    eng.kv.reserve(slot, T + 1)
+    eng.kv.commit()
+    hbm = peaks["hbm_gbs"] * 1e9
+    res = {}
+
+    def timeit(fn, n=5):
+        fn()
+        return statistics.median(ev_time_ms(fn) for _ in range(n))
+
+    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
+        row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ent = torch.tensor([slot, 0, rows, start], dtype=torch.int32, device=dev)
+        x = torch.randn(rows, W, device=dev)
+        hn, hc = torch.empty_like(x), torch.empty(rows, W, dtype=E, device=dev)
+        y = torch.randn(rows, W, device=dev).to(E)
+        P = eng.layers[li_a]
+        ms = timeit(lambda: ops.postnorm_add_norm(y, x, 1.0, 1e-6, hn, 1.0))
+        res[f"{tag}_postnorm_add_norm"] = {"ms": round(ms, 4), "of_hbm": round(rows * W * (2 + 4 + 4 + 4) / (ms / 1e3) / hbm, 3)}
+        ms = timeit(lambda: ops.causal_conv_ragged(hn, eng.slots[("tail1", li_a)], P["canon1"], row_ent, ent, hc))
+        res[f"{tag}_conv"] = {"ms": round(ms, 4), "of_hbm": round(rows * W * (4 + 2) / (ms / 1e3) / hbm, 3)}
+        # attention
+        m = att
+        n_proj = P["w_proj"].shape[0]
+        proj = (0.5 * torch.randn(rows, n_proj, device=dev)).to(E)
+        qbuf = torch.empty(rows, m.heads * m.dim, device=dev)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        kc, vc = eng.kv.k[eng.kv_index[li_a]], eng.kv.v[eng.kv_index[li_a]]
+        cq, sq = eng._table(m.rot_base, m.rot_dims, m.rot_scaling)
+        cv, sv = eng._table(m.rot_base, m.vdim, None)
+        off = P["off"]
+        prep = lambda: ops.attn_prep_append(proj, qbuf, kc, vc, row_ent, ent, eng.kv.page_table, m.heads, m.kv_heads,  # noqa: E731
+                                            m.dim, m.vdim, m.rot_dims, off["q"], off["k"], off["v"], P["q_norm"],
+                                            P["k_norm"], 1e-6, cq, sq, cv, sv)
+        run = lambda: ops.attn_ragged(qbuf, kc, vc, proj, mix, row_ent, ent, eng.kv.page_table, m.heads, m.kv_heads,  # noqa: E731
+                                      m.dim, m.vdim, m.scale, chunk=m.chunk, sink=P["sink"], g_off=off["g"], cos_v=cv, sin_v=sv)
+        ms = timeit(prep)
+        res[f"{tag}_attn_prep"] = {"ms": round(ms, 4)}
+        ms = timeit(run)
+        if rows == 1:
+            byt = (start + 1) * m.kv_heads * (m.dim + m.vdim) * 2
+            res[f"{tag}_attn"] = {"ms": round(ms, 4), "of_hbm": round(byt / (ms / 1e3) / hbm, 3)}
+        else:
+            fl = 2 * (rows * rows // 2) * m.heads * (m.dim + m.vdim)
+            res[f"{tag}_attn"] = {"ms": round(ms, 4), "of_bf16_peak": round(fl / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        # recurrent layer
+        m, P = rec, eng.layers[li_r]
+        n_proj = P["w_proj"].shape[0]
+        proj = (0.5 * torch.randn(rows, n_proj, device=dev)).to(E)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        oscr = torch.empty(rows * m.heads * m.vdim, device=dev)
+        off = P["off"]
+        ms = timeit(lambda: ops.mlstm_ragged(proj, oscr, mix, ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"],
+                                             off["i"], off["f"], off["g"], P["i_b"], P["f_b"], m.gate_cap, P["out_norm"],
+                                             1e-6, eng.slots[("S", li_r)], eng.slots[("n", li_r)], eng.slots[("m", li_r)]))
+        state = m.heads * m.dim * m.vdim * 4
+        if rows == 1:
+            res[f"{tag}_mlstm"] = {"ms": round(ms, 4), "of_hbm": round(2 * state / (ms / 1e3) / hbm, 3)}
+        else:
+            fl = rows * m.heads * m.dim * m.vdim * 4
+            res[f"{tag}_mlstm"] = {"ms": round(ms, 4), "state_update_tflops": round(fl / (ms / 1e3) / 1e12, 3)}
+    eng.close_sequence(slot)
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,6 +583,9 @@ def main():
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--compare-hybrid", action="store_true",
+                    help="instead of the default workload: the layer-by-layer family beside the uniform stack at equal sizes")
+    ap.add_argument("--hybrid-sizes", default="1b,8b")
     args = ap.parse_args()
 
     from dli_b200.engine import NAMED_SPECS
@@ -418,6 +600,10 @@ def main():
         return
 
     peaks = measured_peaks()
+    if args.compare_hybrid:
+        if rank == 0:
+            print(json.dumps(run_hybrid_compare(args, peaks)), flush=True)
+        return
     if world > 1 or args.gpus > 1:
         from dli_b200.pipeline import run_pipeline_bench
 

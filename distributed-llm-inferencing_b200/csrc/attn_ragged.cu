@@ -16,7 +16,7 @@
 // page_table[slot * max_pages + p] is the page of positions p*page_size .. of the sequence in that slot.
 #include <math.h>
 
-#include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace dli {
 
@@ -217,6 +217,213 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
   }
 }
 
+// ---- portions of prompts: the same attention on the tensor cores (bf16 caches) ---------------------------------
+// One CTA per (64-row query tile of one entry, query head); 4 warps x 16 rows; key/value tiles of 64 positions
+// (aligned to multiples of 64 in the sequence) staged from the pages with 16-byte cp.async, double-buffered and
+// XOR-swizzled, and consumed by m16n8k16 MMAs with an fp32 online softmax, as the uniform stacks' prefill kernel
+// does (attn_prefill.cu).  Differences: queries come normed and rotated from qbuf (fp32, rounded to bf16 here);
+// key and value sizes are independent; the mask is per row [lo(row), row] with lo from the chunk and the window;
+// the running maximum starts at the sink (in score units) with weight 1; the epilogue turns each output pair back
+// by the row's position and applies the head's gate.  tiles[2t] = entry, tiles[2t+1] = first row of the tile
+// within the entry.
+constexpr int kRtThreads = 128;
+constexpr int kRtTile = 64;
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(kRtThreads)
+attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                      const bf16* __restrict__ proj, bf16* __restrict__ out, const int32_t* __restrict__ tiles,
+                      AttnRun a) {
+  constexpr int RBK = DK * 2, RBV = DV * 2, CHK = DK / 8, CHV = DV / 8;
+  constexpr int kQBytes = kRtTile * RBK, kKBytes = kRtTile * RBK, kVBytes = kRtTile * RBV;
+  extern __shared__ __align__(128) uint8_t smem_tc[];
+  const uint32_t sQ = smem_u32(smem_tc);
+  const uint32_t sK = sQ + kQBytes;
+  const uint32_t sV = sK + 2 * kKBytes;
+  pdl_wait();
+  pdl_trigger();
+  const int h = blockIdx.x, tile_id = gridDim.y - 1 - blockIdx.y;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[tiles[2 * tile_id]];  // slot, row0, n, start
+  const int q0 = tiles[2 * tile_id + 1];
+  const int g = h / (a.H / a.G);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t* pt = a.page_table + (size_t)e.x * a.max_pages;
+  const int n_rows = min(kRtTile, e.z - q0);
+  const int p0 = e.w + q0, p_last = p0 + n_rows - 1;
+
+  // queries: fp32 -> bf16 into the swizzled tile
+  for (int id = tid; id < kRtTile * CHK; id += kRtThreads) {
+    const int row = id / CHK, c = id - row * CHK;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (row < n_rows) {
+      const float4* src = reinterpret_cast<const float4*>(qbuf + ((size_t)(e.y + q0 + row) * a.H + h) * DK + c * 8);
+      const float4 f0 = src[0], f1 = src[1];
+      u.x = pack_bf16(f0.x, f0.y); u.y = pack_bf16(f0.z, f0.w); u.z = pack_bf16(f1.x, f1.y); u.w = pack_bf16(f1.z, f1.w);
+    }
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + swz<RBK>(row, c)), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w));
+  }
+  auto load_tile = [&](int tile, int stage) {
+    const uint32_t dK = sK + stage * kKBytes, dV = sV + stage * kVBytes;
+    for (int id = tid; id < kRtTile * CHK; id += kRtThreads) {
+      const int row = id / CHK, c = id - row * CHK;
+      const int tok = tile * kRtTile + row;
+      const bool valid = tok <= p_last;
+      size_t off = 0;
+      if (valid) off = (((size_t)pt[tok / a.page_size] * a.G + g) * a.page_size + tok % a.page_size) * DK + c * 8;
+      cp_async_16B(dK + swz<RBK>(row, c), kc + off, valid ? 16 : 0);
+    }
+    for (int id = tid; id < kRtTile * CHV; id += kRtThreads) {
+      const int row = id / CHV, c = id - row * CHV;
+      const int tok = tile * kRtTile + row;
+      const bool valid = tok <= p_last;
+      size_t off = 0;
+      if (valid) off = (((size_t)pt[tok / a.page_size] * a.G + g) * a.page_size + tok % a.page_size) * DV + c * 8;
+      cp_async_16B(dV + swz<RBV>(row, c), vc + off, valid ? 16 : 0);
+    }
+  };
+  auto row_lo = [&](int pos) {
+    int lo = 0;
+    if (a.chunk > 0) lo = (pos / a.chunk) * a.chunk;
+    if (a.window > 0 && pos - a.window + 1 > lo) lo = pos - a.window + 1;
+    return lo;
+  };
+  const int t_begin = row_lo(p0) / kRtTile, t_end = p_last / kRtTile + 1;
+  const int gq = lane >> 2, t4 = lane & 3;
+  const int qabs[2] = {p0 + warp * 16 + gq, p0 + warp * 16 + gq + 8};
+  const int qlo[2] = {row_lo(qabs[0]), row_lo(qabs[1])};
+  const float scale_log2 = a.scale * 1.4426950408889634f;
+  // the sink is a score that is not scaled: in units of the raw dot product it is sink / scale
+  const float m0 = a.sink ? a.sink[h] / a.scale : -INFINITY;
+  float m_run[2] = {m0, m0};
+  float l_run[2] = {(a.sink && t4 == 0) ? 1.f : 0.f, (a.sink && t4 == 0) ? 1.f : 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  uint32_t qf[DK / 16][4];
+
+  load_tile(t_begin, 0);
+  cp_async_commit();
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int stage = (tile - t_begin) & 1;
+    if (tile + 1 < t_end) {
+      load_tile(tile + 1, stage ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (tile == t_begin) {
+#pragma unroll
+      for (int kk = 0; kk < DK / 16; ++kk) {
+        const int mi = lane >> 3;
+        ldmatrix_x4(qf[kk], sQ + swz<RBK>(warp * 16 + (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+      }
+    }
+    const uint32_t cK = sK + stage * kKBytes, cV = sV + stage * kVBytes;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DK / 16; ++kk) {
+#pragma unroll
+      for (int jn = 0; jn < 4; ++jn) {
+        uint32_t kf[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4(kf, cK + swz<RBK>(jn * 16 + (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
+        mma_16816(s[2 * jn], qf[kk], kf[0], kf[1]);
+        mma_16816(s[2 * jn + 1], qf[kk], kf[2], kf[3]);
+      }
+    }
+    const int tk0 = tile * kRtTile;
+    if (tk0 + kRtTile - 1 > p0 || tk0 < row_lo(p_last)) {  // the tile touches the diagonal or a lower bound
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int tok = tk0 + j * 8 + 2 * t4 + (x & 1);
+          const int r = x >> 1;
+          if (tok > qabs[r] || tok < qlo[r]) s[j][x] = -INFINITY;
+        }
+    }
+    uint32_t pa[4][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * r], s[j][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = (m_run[r] == -INFINITY) ? 0.f : exp2f((m_run[r] - m_use) * scale_log2);
+      m_run[r] = m_new;
+      float rs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float p0w = exp2f((s[j][2 * r] - m_use) * scale_log2);
+        const float p1w = exp2f((s[j][2 * r + 1] - m_use) * scale_log2);
+        rs += p0w + p1w;
+        pa[j >> 1][(j & 1) * 2 + r] = pack_bf16(p0w, p1w);
+      }
+      l_run[r] = l_run[r] * corr + rs;
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) {
+        o[i][2 * r] *= corr;
+        o[i][2 * r + 1] *= corr;
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int jp = 0; jp < DV / 16; ++jp) {
+        uint32_t vf[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4_trans(vf, cV + swz<RBV>(ks * 16 + (mi & 1) * 8 + (lane & 7), jp * 2 + (mi >> 1)));
+        mma_16816(o[2 * jp], pa[ks], vf[0], vf[1]);
+        mma_16816(o[2 * jp + 1], pa[ks], vf[2], vf[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    const int lr = warp * 16 + gq + r * 8;  // row within the tile
+    if (lr < n_rows) {
+      const size_t row = (size_t)e.y + q0 + lr;
+      const int pos = qabs[r];
+      float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      if (a.g_off >= 0) inv *= 1.f / (1.f + expf(-__bfloat162float(proj[row * a.ldp + a.g_off + h])));
+      bf16* dst = out + (row * a.H + h) * DV + 2 * t4;
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) {
+        float u = o[i][2 * r], v = o[i][2 * r + 1];
+        if (a.cos_v) {
+          const int pr = i * 4 + t4;  // pair index of columns 8i + 2*t4, +1
+          const float c = a.cos_v[(size_t)pos * (DV / 2) + pr], sn = a.sin_v[(size_t)pos * (DV / 2) + pr];
+          const float u2 = u * c + v * sn, v2 = v * c - u * sn;
+          u = u2; v = v2;
+        }
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(u * inv, v * inv);
+      }
+    }
+  }
+}
+
+template <int DK, int DV>
+static int launch_ragged_tc(const float* qbuf, const void* kc, const void* vc, const void* proj, void* out,
+                            const int32_t* tiles, int n_tiles, const AttnRun& a, cudaStream_t s) {
+  constexpr int kSmem = kRtTile * DK * 2 + 2 * kRtTile * (DK + DV) * 2;
+  static PerDeviceOnce once;
+  DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(attn_ragged_tc_kernel<DK, DV>,
+                                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)));
+  DLI_LAUNCH("attn_ragged_tc", (attn_ragged_tc_kernel<DK, DV>), dim3(a.H, n_tiles), dim3(kRtThreads), (size_t)kSmem, s,
+             qbuf, (const bf16*)kc, (const bf16*)vc, (const bf16*)proj, (bf16*)out, tiles, a);
+  return DLI_OK;
+}
+
 }  // namespace dli
 
 using namespace dli;
@@ -261,6 +468,30 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
   if (dt == 0) DLI_LAUNCH("attn_ragged", attn_ragged_kernel<bf16>, dim3(rows, H), dim3(kAttnThreads), smem, s, qbuf, (const bf16*)k_cache, (const bf16*)v_cache, (const bf16*)proj, (bf16*)out, a);
   else DLI_LAUNCH("attn_ragged", attn_ragged_kernel<float>, dim3(rows, H), dim3(kAttnThreads), smem, s, qbuf, (const float*)k_cache, (const float*)v_cache, (const float*)proj, (float*)out, a);
   return DLI_OK;
+}
+
+int dli_attn_ragged_tc_supported(int D, int V, int dt) {
+  return dt == 0 && ((D == 64 && V == 64) || (D == 128 && V == 128) || (D == 64 && V == 128) || (D == 128 && V == 64) ||
+                     (D == 128 && V == 256));
+}
+
+int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
+                       const int32_t* ent, const int32_t* tiles, int n_tiles, const int32_t* page_table, int max_pages,
+                       int page_size, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink,
+                       int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream) {
+  DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && ent && tiles && page_table, "dli_attn_ragged_tc: null pointer");
+  DLI_CHECK_ARG(g_off < 0 || proj, "dli_attn_ragged_tc: a gate needs the projection rows");
+  DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && scale > 0.f, "dli_attn_ragged_tc: H=%d G=%d scale=%g", H, G, scale);
+  if (!dli_attn_ragged_tc_supported(D, V, 0))
+    return dli::fail(DLI_ERR_UNSUPPORTED, "dli_attn_ragged_tc: key size %d with value size %d has no tensor-core tile", D, V);
+  if (n_tiles <= 0) return DLI_OK;
+  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 64 && V == 64) return launch_ragged_tc<64, 64>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
+  if (D == 128 && V == 128) return launch_ragged_tc<128, 128>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
+  if (D == 64 && V == 128) return launch_ragged_tc<64, 128>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
+  if (D == 128 && V == 64) return launch_ragged_tc<128, 64>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
+  return launch_ragged_tc<128, 256>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
 }
 
 }  // extern "C"

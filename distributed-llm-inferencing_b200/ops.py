@@ -544,6 +544,21 @@ def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, 
     return out
 
 
+def attn_ragged_tc_supported(D, V, dtype) -> bool:
+    return dtype == torch.bfloat16 and bool(_lib.load().dli_attn_ragged_tc_supported(int(D), int(V), 0))
+
+
+def attn_ragged_tc(qbuf, k_cache, v_cache, proj, out, ent, tiles, page_table, H, G, D, V, scale, chunk=0, window=0,
+                   sink=None, g_off=-1, cos_v=None, sin_v=None):
+    """attn_ragged for steps with portions of prompts, on the tensor cores: tiles int32 [n_tiles, 2] = (entry, first
+    row of the 64-row query tile within the entry)."""
+    _f32(qbuf, sink, cos_v, sin_v), _i32(ent, tiles, page_table), _req(out), _req(proj), _req(k_cache), _req(v_cache)
+    _call("dli_attn_ragged_tc", 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(ent), _p(tiles),
+          tiles.numel() // 2, _p(page_table), page_table.shape[1], k_cache.shape[2], H, G, D, V, float(scale), int(chunk),
+          int(window), _p(sink), proj.shape[1], g_off, _p(cos_v), _p(sin_v), _stream())
+    return out
+
+
 def mlstm_ragged(proj, o_scratch, out, ent, H, D, V, q_off, k_off, v_off, i_off, f_off, g_off, i_bias, f_bias, cap,
                  out_w, eps, S, n, m):
     """Matrix-memory recurrence over the rows of every entry + head norm, weight and output gate -> out [rows, H*V]."""

@@ -141,6 +141,7 @@ class RaggedEngine:
         self.eos_token_ids: tuple = ()
         self.pad_token_id: Optional[int] = None
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
+        self.tc_min_rows = int(os.environ.get("DLI_RAGGED_TC_MIN_ROWS", "16"))  # portions from this size: tensor-core attention
         self.layer_trace: Optional[list] = None    # set to [] to collect the residual stream after every layer
         ops.set_pdl(os.environ.get("DLI_PDL", "1") == "1")
 
@@ -301,9 +302,15 @@ class RaggedEngine:
             tokens += [int(t) for t in toks]
         if grew:
             self.kv.commit()
-        # one host -> device copy of the step's description: tokens | row_ent | ent | want_rows (16-byte aligned parts)
+        # steps that hold a portion of a prompt run attention in 64-row query tiles on the tensor cores
+        tiles: List[int] = []
+        if self.dtype == BF and any(len(t) >= self.tc_min_rows for _, t in batch):
+            for i, (_, toks) in enumerate(batch):
+                for q0 in range(0, len(toks), 64):
+                    tiles += [i, q0]
+        # one host -> device copy of the step's description: tokens | row_ent | ent | want_rows | tiles (16-byte aligned parts)
         r4, e4, w4 = _ceil(rows, 4), 4 * n_ent, _ceil(max(len(want_rows), 1), 4)
-        total = 2 * r4 + e4 + w4
+        total = 2 * r4 + e4 + w4 + len(tiles)
         if total > self._meta_cap:
             self._meta_cap = _ceil(total, 1024)
             self._meta_host = torch.zeros(self._meta_cap, dtype=torch.int32).pin_memory()
@@ -314,10 +321,13 @@ class RaggedEngine:
         mh[2 * r4:2 * r4 + e4] = torch.tensor(ent, dtype=torch.int32)
         if want_rows:
             mh[2 * r4 + e4:2 * r4 + e4 + len(want_rows)] = torch.tensor(want_rows, dtype=torch.int32)
+        if tiles:
+            mh[2 * r4 + e4 + w4:total] = torch.tensor(tiles, dtype=torch.int32)
         md = self._meta_dev
         md[:total].copy_(mh[:total], non_blocking=True)
         d_tok, d_rent, d_ent = md[:rows], md[r4:r4 + rows], md[2 * r4:2 * r4 + e4]
         d_want = md[2 * r4 + e4:2 * r4 + e4 + len(want_rows)]
+        d_tiles = md[2 * r4 + e4 + w4:total]
 
         self._workspace(rows)
         W = s.width
@@ -346,8 +356,14 @@ class RaggedEngine:
                 ops.attn_prep_append(proj, qbuf, kc, vc, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
                                      m.rot_dims, off["q"], off["k"], off["v"], P["q_norm"], P["k_norm"], s.eps,
                                      cq, sq, cv, sv)
-                ops.attn_ragged(qbuf, kc, vc, proj, mix, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
-                                m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv, sin_v=sv)
+                if tiles and m.scale > 0 and ops.attn_ragged_tc_supported(m.dim, m.vdim, E):
+                    ops.attn_ragged_tc(qbuf, kc, vc, proj, mix, d_ent, d_tiles, pt, m.heads, m.kv_heads, m.dim, m.vdim,
+                                       m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"],
+                                       cos_v=cv, sin_v=sv)
+                else:
+                    ops.attn_ragged(qbuf, kc, vc, proj, mix, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
+                                    m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv,
+                                    sin_v=sv)
             else:
                 oscr = self._oscr[:rows * n_mix]
                 ops.mlstm_ragged(proj, oscr, mix, d_ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"], off["i"],

@@ -436,6 +436,15 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
                     int g_off, const float* cos_v, const float* sin_v, int dt, dli_stream_t stream);
 
+/* The same attention for steps that hold portions of prompts, on the tensor cores (bf16 caches only): one CTA per
+ * 64-row query tile of an entry and query head; tiles[2t] = entry, tiles[2t+1] = first row of the tile within the
+ * entry.  dli_attn_ragged_tc_supported says whether (key size, value size, element type) has a tile. */
+int dli_attn_ragged_tc_supported(int D, int V, int dt);
+int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
+                       const int32_t* ent, const int32_t* tiles, int n_tiles, const int32_t* page_table, int max_pages,
+                       int page_size, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink,
+                       int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream);
+
 /* Matrix-memory recurrent layer (mLSTM, stabilised): q, k, v, gate pre-activations and the output gate are columns
  * of proj [rows, ldp]; state S [slots, H, D, V], n [slots, H, D], m [slots, H] fp32 is read and advanced (an entry
  * at position 0 starts from zero); o_scratch [rows, H, V] fp32; y [rows, H*V] = o / rms_head(o) * out_w * sigmoid(g). */

@@ -241,3 +241,20 @@ def test_scheduler_requests_of_unequal_length_and_sampling_is_keyed_by_position(
     # seeds follow the submission order in run(); alone[i] used seed 7, so compare the first request only for tokens
     assert together[0] == alone[0]
     assert [len(t) for t in together] == [26, 10, 14]
+
+
+def test_bfloat16_portions_on_the_tensor_core_attention():
+    """Head sizes that have a tensor-core tile: portions of 16 rows and more take that kernel, shorter steps the
+    row-wise one; both against the oracle and against each other."""
+    cfg = config([(attn(heads=4, kv=2, dim=64, vdim=64, chunk=50, rot_dims=32, scale=0.125), 128), (mlstm(), 0),
+                  (attn(heads=2, kv=1, dim=64, vdim=128, chunk=33, rot_dims=64, scale=0.125), 0)], width=128)
+    eng, sd = build(cfg, torch.bfloat16, max_seq_len=256, page_size=16)
+    toks = prompt(170, cfg["vocab"], 6)
+    ref = R.forward(cfg, sd, toks)
+    whole = run_schedule(eng, toks, [170])
+    parts = run_schedule(eng, toks, [70, 3, 64, 20])
+    eng.tc_min_rows = 10 ** 9
+    rowwise = run_schedule(eng, toks, [170])
+    for got in (whole, parts, rowwise):
+        assert rel_err(got, ref).max() < TOL16
+    assert rel_err(whole, rowwise.double()).max() < TOL16 / 2

@@ -103,7 +103,7 @@ def attn_oracle(q, k, v, g, m, sink, qn, kn, eps):
     return R.attention_mixer(h, P, "", m, eps)
 
 
-def run_attn(q, k, v, g, m, sink, qn, kn, eps, cuts, page_size, dt=torch.float32, window=0):
+def run_attn(q, k, v, g, m, sink, qn, kn, eps, cuts, page_size, dt=torch.float32, window=0, tc=False):
     """The kernels on one sequence cut into portions `cuts`, pages handed out in a scrambled order."""
     from dli_b200 import ops
     from dli_b200.ragged_engine import rot_frequencies
@@ -135,8 +135,13 @@ def run_attn(q, k, v, g, m, sink, qn, kn, eps, cuts, page_size, dt=torch.float32
         ops.attn_prep_append(pr, qbuf, kc, vc, row_ent, ent, pt, H, G, D, V, rot["dims"], 0, H * D, H * D + G * D,
                              qn.float().to(DEV), kn.float().to(DEV), eps, cq, sq, cv, sv)
         o = torch.empty(n, H * V, dtype=dt, device=DEV)
-        ops.attn_ragged(qbuf, kc, vc, pr, o, row_ent, ent, pt, H, G, D, V, m["scale"], chunk=m["mask"]["size"],
-                        window=window, sink=sink.float().to(DEV), g_off=H * D + G * D + G * V, cos_v=cv, sin_v=sv)
+        if tc:
+            tiles = torch.tensor([[0, q0] for q0 in range(0, n, 64)], dtype=torch.int32, device=DEV)
+            ops.attn_ragged_tc(qbuf, kc, vc, pr, o, ent, tiles, pt, H, G, D, V, m["scale"], chunk=m["mask"]["size"],
+                               window=window, sink=sink.float().to(DEV), g_off=H * D + G * D + G * V, cos_v=cv, sin_v=sv)
+        else:
+            ops.attn_ragged(qbuf, kc, vc, pr, o, row_ent, ent, pt, H, G, D, V, m["scale"], chunk=m["mask"]["size"],
+                            window=window, sink=sink.float().to(DEV), g_off=H * D + G * D + G * V, cos_v=cv, sin_v=sv)
         out[at:at + n] = o
         at += n
     assert at == T
@@ -188,6 +193,52 @@ def test_attention_one_key_stands_out(cuts, target):
     vj_at_i = R.turn_pairs(R.turn_pairs(v[j].double(), av[j]), -av[i]) * 0.5   # gate sigmoid(0)
     close = (ref[i, :8] - vj_at_i).abs().max() < 1e-3
     assert bool(close) == inside
+
+
+@pytest.mark.parametrize("dims", [(64, 64), (128, 128), (64, 128), (128, 256)])
+@pytest.mark.parametrize("cuts", [[230], [100, 3, 64, 63], [17, 1, 130, 2, 80]])
+def test_attention_tensor_core_tiles_against_oracle(dims, cuts):
+    """The tensor-core kernel on portions that start anywhere (also single rows beside them): chunk edges that are no
+    multiple of the tile, pages smaller than the tile, grouped heads, sink, gate, value rotation; bf16 operands."""
+    D, V = dims
+    torch.manual_seed(7)
+    m = {"heads": 4, "kv_heads": 2, "dim": D, "vdim": V, "scale": D ** -0.5, "mask": {"size": 75},
+         "rot": {"base": 1000.0, "dims": D // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}}}
+    T = 230
+    bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731  (inputs that bf16 holds exactly)
+    q, k = bf(torch.randn(T, 4 * D)), bf(torch.randn(T, 2 * D))
+    v, g = bf(torch.randn(T, 2 * V)), bf(torch.randn(T, 4))
+    sink, qn, kn = torch.randn(4), torch.rand(D) + 0.5, torch.rand(D) + 0.5
+    ref = attn_oracle(q, k, v, g, m, sink, qn, kn, 1e-5)
+    got = run_attn(q, k, v, g, m, sink, qn, kn, 1e-5, cuts, page_size=16, dt=torch.bfloat16, tc=True)
+    plain = run_attn(q, k, v, g, m, sink, qn, kn, 1e-5, cuts, page_size=16, dt=torch.bfloat16, tc=False)
+    assert (got.double().cpu() - ref).abs().max() < 0.03
+    assert (plain.double().cpu() - ref).abs().max() < 0.03
+    assert (got.double().cpu() - ref).pow(2).mean().sqrt() < 0.004
+
+
+@pytest.mark.parametrize("j", [149, 150, 212])
+def test_attention_tensor_core_one_key_stands_out(j):
+    """Query 220 (chunk 150..224) against ONE matching key: the last position of the previous chunk (never seen), the
+    first of its own, and one in the middle; bf16 rounding cannot hide a weight of one."""
+    torch.manual_seed(8)
+    D = V = 64
+    m = {"heads": 2, "kv_heads": 1, "dim": D, "vdim": V, "scale": 4.0, "mask": {"size": 75}, "rot": {"base": 50.0, "dims": 2}}
+    T, i = 230, 220
+    q, k = torch.randn(T, 2 * D), torch.randn(T, D)
+    v, g = torch.randn(T, V).to(torch.bfloat16).float(), torch.zeros(T, 2)
+    k[:, 3] = 0
+    q[i, :D] = 0
+    q[i, 3] = 1.0
+    k[j] = 0
+    k[j, 3] = 1.0
+    sink, ones = torch.tensor([-30.0, -30.0]), torch.ones(D)
+    ref = attn_oracle(q, k, v, g, m, sink, ones, ones, 1e-6)
+    got = run_attn(q, k, v, g, m, sink, ones, ones, 1e-6, [130, 100], page_size=16, dt=torch.bfloat16, tc=True)
+    assert (got.double().cpu()[i] - ref[i]).abs().max() < 0.02
+    av = torch.arange(T, dtype=torch.float64)[:, None] * R.frequencies(50.0, V)[None]
+    vj_at_i = R.turn_pairs(R.turn_pairs(v[j].double(), av[j]), -av[i]) * 0.5
+    assert bool((got.double().cpu()[i, :V] - vj_at_i).abs().max() < 0.02) == (j >= 150)
 
 
 def test_attention_sink_takes_weight_and_window_option():
