@@ -544,6 +544,10 @@ def hybrid_kernel_times(eng, spec, T, peaks):
                                       m.dim, m.vdim, m.scale, chunk=m.chunk, sink=P["sink"], g_off=off["g"], cos_v=cv, sin_v=sv)
         ms = timeit(prep)
         res[f"{tag}_attn_prep"] = {"ms": round(ms, 4)}
+        if rows > 1 and ops.attn_ragged_tc_supported(m.dim, m.vdim, E):
+            tiles = torch.tensor([[0, q0] for q0 in range(0, rows, 64)], dtype=torch.int32, device=dev)
+            run = lambda: ops.attn_ragged_tc(qbuf, kc, vc, proj, mix, ent, tiles, eng.kv.page_table, m.heads, m.kv_heads,  # noqa: E731
+                                             m.dim, m.vdim, m.scale, chunk=m.chunk, sink=P["sink"], g_off=off["g"], cos_v=cv, sin_v=sv)
         ms = timeit(run)
         if rows == 1:
             byt = (start + 1) * m.kv_heads * (m.dim + m.vdim) * 2
@@ -560,7 +564,8 @@ def hybrid_kernel_times(eng, spec, T, peaks):
         off = P["off"]
         ms = timeit(lambda: ops.mlstm_ragged(proj, oscr, mix, ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"],
                                              off["i"], off["f"], off["g"], P["i_b"], P["f_b"], m.gate_cap, P["out_norm"],
-                                             1e-6, eng.slots[("S", li_r)], eng.slots[("n", li_r)], eng.slots[("m", li_r)]))
+                                             1e-6, eng.slots[("S", li_r)], eng.slots[("n", li_r)], eng.slots[("m", li_r)],
+                                             blocked=rows > 1))
         state = m.heads * m.dim * m.vdim * 4
         if rows == 1:
             res[f"{tag}_mlstm"] = {"ms": round(ms, 4), "of_hbm": round(2 * state / (ms / 1e3) / hbm, 3)}

@@ -83,7 +83,7 @@ SIGNATURES = {
     "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
                                 _i, _vp, _vp, _vp]),
     "dli_mlstm_ragged": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp,
-                              _f, _vp, _vp, _vp, _i, _vp]),
+                              _f, _vp, _vp, _vp, _i, _i, _vp]),
 }
 
 

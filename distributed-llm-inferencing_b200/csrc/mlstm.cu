@@ -115,6 +115,190 @@ mlstm_scan_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs a
   }
 }
 
+// ---- portions of prompts: the same recurrence, 64 positions at a time ------------------------------------------
+// Within a block of L positions (t = 1..L) let b_t be the running sum of the log forget gates, a_s = i_s - b_s and
+// M_t = max(m_0, max_{s<=t} a_s).  Unrolling the recurrence gives m_t = b_t + M_t and
+//     S_t = e^{m_0 - M_t} S_0 + sum_{s<=t} e^{a_s - M_t} k_s v_s^T          (n_t likewise)
+// so the read-outs of the whole block are two small matrix products, (Q K^T masked and weighted by e^{a_s - M_t}) V
+// plus e^{m_0 - M_t} Q S_0, and the state moves once per block: S_L = e^{m_0 - M_L} S_0 + K^T diag(e^{a_s - M_L}) V.
+// Every exponent is <= 0.  All of it fp32 on the CUDA cores (the state and what enters it stay in 32-bit).
+// One CTA per (entry, head, 64-column slice of V); q and k of the block are held transposed in shared memory.
+constexpr int kMcL = 64, kMcLp = 68, kMcCols = 64, kMcThreads = 256;
+
+template <typename E>
+__global__ void __launch_bounds__(kMcThreads)
+mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs a) {
+  extern __shared__ __align__(16) float smc[];
+  const int D = a.D;
+  float* qT = smc;                          // [D][kMcLp]
+  float* kT = qT + (size_t)D * kMcLp;       // [D][kMcLp]
+  float* Ss = kT + (size_t)D * kMcLp;       // [D][kMcCols]
+  float* AT = Ss + (size_t)D * kMcCols;     // [L][kMcLp]   AT[s][t]
+  float* vs = AT + kMcL * kMcLp;            // [L][kMcCols]
+  float* ns = vs + kMcL * kMcCols;          // [D]
+  float* av = ns + D;                       // [L] a_s
+  float* Mv = av + kMcL;                    // [L] M_t
+  float* bv = Mv + kMcL;                    // [L] b_t
+  float* qn = bv + kMcL;                    // [L] n . q per row
+  pdl_wait();
+  pdl_trigger();
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[blockIdx.x];
+  const int h = blockIdx.y, c0 = blockIdx.z * kMcCols;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const bool fresh = e.w == 0;
+  float* Sg = a.S + ((size_t)e.x * a.H + h) * D * a.V;
+  float* ng = a.n + ((size_t)e.x * a.H + h) * D;
+  float* mg = a.m + (size_t)e.x * a.H + h;
+  for (int i = tid; i < D * kMcCols; i += kMcThreads) {
+    const int d = i / kMcCols, c = c0 + i % kMcCols;
+    Ss[i] = (fresh || c >= a.V) ? 0.f : Sg[(size_t)d * a.V + c];
+  }
+  for (int d = tid; d < D; d += kMcThreads) ns[d] = fresh ? 0.f : ng[d];
+  float m0 = fresh ? 0.f : *mg;
+  const float qscale = 1.f / sqrtf((float)D);
+  const float ib = a.i_bias ? a.i_bias[h] : 0.f, fb = a.f_bias ? a.f_bias[h] : 0.f;
+  __syncthreads();
+
+  for (int t0 = 0; t0 < e.z; t0 += kMcL) {
+    const int len = min(kMcL, e.z - t0);
+    const E* base = proj + (size_t)(e.y + t0) * a.ldp;
+    // q, k transposed (zero beyond len), v slice, gates
+    for (int i = tid; i < kMcL * D; i += kMcThreads) {
+      const int t = i / D, d = i - t * D;
+      float qv = 0.f, kv = 0.f;
+      if (t < len) {
+        qv = m_to_f(base[(size_t)t * a.ldp + a.q_off + h * D + d]) * qscale;
+        kv = m_to_f(base[(size_t)t * a.ldp + a.k_off + h * D + d]);
+      }
+      qT[d * kMcLp + t] = qv;
+      kT[d * kMcLp + t] = kv;
+    }
+    for (int i = tid; i < kMcL * kMcCols; i += kMcThreads) {
+      const int t = i / kMcCols, c = c0 + i % kMcCols;
+      vs[i] = (t < len && c < a.V) ? m_to_f(base[(size_t)t * a.ldp + a.v_off + h * a.V + c]) : 0.f;
+    }
+    if (tid < kMcL) {
+      float ig = -INFINITY, fg = 0.f;
+      if (tid < len) {
+        ig = soft_cap(m_to_f(base[(size_t)tid * a.ldp + a.i_off + h]) + ib, a.cap);
+        fg = log_sigmoid(soft_cap(m_to_f(base[(size_t)tid * a.ldp + a.f_off + h]) + fb, a.cap));
+      }
+      av[tid] = ig;   // for now: i_s
+      bv[tid] = fg;   // for now: f_s
+    }
+    __syncthreads();
+    if (tid == 0) {  // 64 steps: running sums and maxima in order
+      float b = 0.f, M = m0;
+      for (int t = 0; t < kMcL; ++t) {
+        b += bv[t];
+        const float as = av[t] - b;
+        M = fmaxf(M, as);
+        bv[t] = b; av[t] = as; Mv[t] = M;
+      }
+    }
+    __syncthreads();
+    // AT[s][t] = (q_t . k_s) e^{a_s - M_t} for s <= t, else 0: rows t = 4ty.., columns s = 4tx..
+    {
+      float acc[4][4] = {};
+      for (int d = 0; d < D; ++d) {
+        const float4 qa = *reinterpret_cast<const float4*>(qT + d * kMcLp + 4 * ty);
+        const float4 kb = *reinterpret_cast<const float4*>(kT + d * kMcLp + 4 * tx);
+        const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, kv[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qv[i], kv[j], acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int t = 4 * ty + i, sidx = 4 * tx + j;
+          AT[sidx * kMcLp + t] = (sidx <= t) ? acc[i][j] * expf(av[sidx] - Mv[t]) : 0.f;
+        }
+    }
+    // n . q of the incoming state, per row
+    if (tid < kMcL) {
+      float d0 = 0.f;
+      for (int d = 0; d < D; ++d) d0 = fmaf(ns[d], qT[d * kMcLp + tid], d0);
+      qn[tid] = d0;
+    }
+    __syncthreads();
+    // read-out: rows t = 4ty.., columns c = 4tx..
+    {
+      float inter[4][4] = {}, intra[4][4] = {};
+      for (int d = 0; d < D; ++d) {
+        const float4 qa = *reinterpret_cast<const float4*>(qT + d * kMcLp + 4 * ty);
+        const float4 sb = *reinterpret_cast<const float4*>(Ss + d * kMcCols + 4 * tx);
+        const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, sv[4] = {sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) inter[i][j] = fmaf(qv[i], sv[j], inter[i][j]);
+      }
+      float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int sidx = 0; sidx < len; ++sidx) {
+        const float4 aa = *reinterpret_cast<const float4*>(AT + sidx * kMcLp + 4 * ty);
+        const float4 vb = *reinterpret_cast<const float4*>(vs + sidx * kMcCols + 4 * tx);
+        const float aw[4] = {aa.x, aa.y, aa.z, aa.w}, vv[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          rowsum[i] += aw[i];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) intra[i][j] = fmaf(aw[i], vv[j], intra[i][j]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = 4 * ty + i;
+        if (t >= len) continue;
+        const float g = expf(m0 - Mv[t]);
+        const float den = fmaxf(fabsf(g * qn[t] + rowsum[i]), expf(-(bv[t] + Mv[t]))) + 1e-6f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = c0 + 4 * tx + j;
+          if (c < a.V) o[((size_t)(e.y + t0 + t) * a.H + h) * a.V + c] = (g * inter[i][j] + intra[i][j]) / den;
+        }
+      }
+    }
+    __syncthreads();
+    // the state moves to the end of the block
+    {
+      const float ML = Mv[kMcL - 1], gL = expf(m0 - ML);
+      for (int d = ty; d < D; d += 16) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float nacc = 0.f;
+        for (int sidx = 0; sidx < len; ++sidx) {
+          const float u = expf(av[sidx] - ML) * kT[d * kMcLp + sidx];
+          const float4 vb = *reinterpret_cast<const float4*>(vs + sidx * kMcCols + 4 * tx);
+          acc[0] = fmaf(u, vb.x, acc[0]); acc[1] = fmaf(u, vb.y, acc[1]);
+          acc[2] = fmaf(u, vb.z, acc[2]); acc[3] = fmaf(u, vb.w, acc[3]);
+          nacc += u;
+        }
+        float4* sp = reinterpret_cast<float4*>(Ss + d * kMcCols + 4 * tx);
+        float4 sv = *sp;
+        sv.x = gL * sv.x + acc[0]; sv.y = gL * sv.y + acc[1]; sv.z = gL * sv.z + acc[2]; sv.w = gL * sv.w + acc[3];
+        *sp = sv;
+        if (tx == 0) ns[d] = gL * ns[d] + nacc;
+      }
+      m0 = bv[kMcL - 1] + ML;
+    }
+    __syncthreads();
+  }
+  for (int i = tid; i < D * kMcCols; i += kMcThreads) {
+    const int d = i / kMcCols, c = c0 + i % kMcCols;
+    if (c < a.V) Sg[(size_t)d * a.V + c] = Ss[i];
+  }
+  if (blockIdx.z == 0) {
+    for (int d = tid; d < D; d += kMcThreads) ng[d] = ns[d];
+    if (tid == 0) *mg = m0;
+  }
+}
+
+static size_t mlstm_chunk_smem(int D) {
+  return sizeof(float) * (2 * (size_t)D * kMcLp + (size_t)D * kMcCols + kMcL * kMcLp + kMcL * kMcCols + D + 4 * kMcL);
+}
+
 // y[row, h, :] = o / rms(o over the head) * w[h, :] * sigmoid(gate[row, h, :]); one warp per (row, head).
 template <typename E>
 __global__ void __launch_bounds__(128)
@@ -145,7 +329,7 @@ extern "C" {
 int dli_mlstm_ragged(const void* proj, float* o_scratch, void* y, const int32_t* ent, int n_ent, int rows, int H, int D,
                      int V, int ldp, int q_off, int k_off, int v_off, int i_off, int f_off, int g_off,
                      const float* i_bias, const float* f_bias, float cap, const float* out_w, float eps, float* S,
-                     float* n, float* m, int dt, dli_stream_t stream) {
+                     float* n, float* m, int blocked, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(proj && o_scratch && y && ent && out_w && S && n && m, "dli_mlstm_ragged: null pointer");
   DLI_CHECK_ARG(H > 0 && D > 0 && V > 0, "dli_mlstm_ragged: empty shape");
   DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_mlstm_ragged: ent must be 16-byte aligned");
@@ -156,15 +340,22 @@ int dli_mlstm_ragged(const void* proj, float* o_scratch, void* y, const int32_t*
   DLI_CHECK_ARG(smem <= 200 * 1024, "dli_mlstm_ragged: key size %d needs %zu bytes of shared memory", D, smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(n_ent, H, (V + kMlCols - 1) / kMlCols);
+  const size_t csmem = mlstm_chunk_smem(D);
+  const bool chunked = blocked && csmem <= 220 * 1024;  // larger key sizes: the token-by-token kernel
+  const dim3 cgrid(n_ent, H, (V + kMcCols - 1) / kMcCols);
   if (dt == 0) {
     static PerDeviceOnce once;
-    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
-    DLI_LAUNCH("mlstm_scan", mlstm_scan_kernel<bf16>, grid, dim3(kMlThreads), smem, s, (const bf16*)proj, o_scratch, a);
+    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                        DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_chunk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
+    if (chunked) DLI_LAUNCH("mlstm_chunk", mlstm_chunk_kernel<bf16>, cgrid, dim3(kMcThreads), csmem, s, (const bf16*)proj, o_scratch, a);
+    else DLI_LAUNCH("mlstm_scan", mlstm_scan_kernel<bf16>, grid, dim3(kMlThreads), smem, s, (const bf16*)proj, o_scratch, a);
     DLI_LAUNCH("mlstm_out", mlstm_out_kernel<bf16>, dim3((rows * H + 3) / 4), dim3(128), 0, s, (const float*)o_scratch, (const bf16*)proj, out_w, (bf16*)y, rows, H, V, ldp, g_off, eps);
   } else {
     static PerDeviceOnce once;
-    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
-    DLI_LAUNCH("mlstm_scan", mlstm_scan_kernel<float>, grid, dim3(kMlThreads), smem, s, (const float*)proj, o_scratch, a);
+    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                        DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
+    if (chunked) DLI_LAUNCH("mlstm_chunk", mlstm_chunk_kernel<float>, cgrid, dim3(kMcThreads), csmem, s, (const float*)proj, o_scratch, a);
+    else DLI_LAUNCH("mlstm_scan", mlstm_scan_kernel<float>, grid, dim3(kMlThreads), smem, s, (const float*)proj, o_scratch, a);
     DLI_LAUNCH("mlstm_out", mlstm_out_kernel<float>, dim3((rows * H + 3) / 4), dim3(128), 0, s, (const float*)o_scratch, (const float*)proj, out_w, (float*)y, rows, H, V, ldp, g_off, eps);
   }
   return DLI_OK;

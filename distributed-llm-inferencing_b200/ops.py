@@ -560,10 +560,10 @@ def attn_ragged_tc(qbuf, k_cache, v_cache, proj, out, ent, tiles, page_table, H,
 
 
 def mlstm_ragged(proj, o_scratch, out, ent, H, D, V, q_off, k_off, v_off, i_off, f_off, g_off, i_bias, f_bias, cap,
-                 out_w, eps, S, n, m):
+                 out_w, eps, S, n, m, blocked=False):
     """Matrix-memory recurrence over the rows of every entry + head norm, weight and output gate -> out [rows, H*V]."""
     _req(proj, proj.dtype), _req(out, proj.dtype), _f32(o_scratch, i_bias, f_bias, out_w, S, n, m), _i32(ent)
     _call("dli_mlstm_ragged", 2, _p(proj), _p(o_scratch), _p(out), _p(ent), ent.numel() // 4, proj.shape[0], H, D, V,
           proj.shape[1], q_off, k_off, v_off, i_off, f_off, g_off, _p(i_bias), _p(f_bias), float(cap), _p(out_w),
-          float(eps), _p(S), _p(n), _p(m), _dt(proj), _stream())
+          float(eps), _p(S), _p(n), _p(m), int(bool(blocked)), _dt(proj), _stream())
     return out

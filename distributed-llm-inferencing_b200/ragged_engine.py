@@ -330,6 +330,7 @@ class RaggedEngine:
         d_tiles = md[2 * r4 + e4 + w4:total]
 
         self._workspace(rows)
+        long_step = any(len(t) >= self.tc_min_rows for _, t in batch)  # a portion of a prompt is in the step
         W = s.width
         x, hn, hc = self._x[:rows], self._hn[:rows], self._hc[:rows]
         y = self._y[:rows]
@@ -368,7 +369,7 @@ class RaggedEngine:
                 oscr = self._oscr[:rows * n_mix]
                 ops.mlstm_ragged(proj, oscr, mix, d_ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"], off["i"],
                                  off["f"], off["g"], P["i_b"], P["f_b"], m.gate_cap, P["out_norm"], s.eps,
-                                 self.slots[("S", li)], self.slots[("n", li)], self.slots[("m", li)])
+                                 self.slots[("S", li)], self.slots[("n", li)], self.slots[("m", li)], blocked=long_step)
             self._lin(mix, P["wo"], y)
             g_post = P["norm1b"]
             if L.ff:

@@ -447,11 +447,13 @@ int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cac
 
 /* Matrix-memory recurrent layer (mLSTM, stabilised): q, k, v, gate pre-activations and the output gate are columns
  * of proj [rows, ldp]; state S [slots, H, D, V], n [slots, H, D], m [slots, H] fp32 is read and advanced (an entry
- * at position 0 starts from zero); o_scratch [rows, H, V] fp32; y [rows, H*V] = o / rms_head(o) * out_w * sigmoid(g). */
+ * at position 0 starts from zero); o_scratch [rows, H, V] fp32; y [rows, H*V] = o / rms_head(o) * out_w * sigmoid(g).
+ * blocked != 0 (steps with portions of prompts): the recurrence is evaluated 64 positions at a time as small matrix
+ * products; 0: token by token (decode steps).  The two agree up to fp32 rounding. */
 int dli_mlstm_ragged(const void* proj, float* o_scratch, void* y, const int32_t* ent, int n_ent, int rows, int H, int D,
                      int V, int ldp, int q_off, int k_off, int v_off, int i_off, int f_off, int g_off,
                      const float* i_bias, const float* f_bias, float cap, const float* out_w, float eps, float* S,
-                     float* n, float* m, int dt, dli_stream_t stream);
+                     float* n, float* m, int blocked, int dt, dli_stream_t stream);
 
 #ifdef __cplusplus
 }

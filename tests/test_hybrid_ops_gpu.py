@@ -272,8 +272,11 @@ def mlstm_oracle(q, k, v, g, ig, fg, m, ib, fb, nw, eps):
 
 
 @pytest.mark.parametrize("dims", [(2, 48, 64), (3, 10, 40), (1, 130, 33)])
-@pytest.mark.parametrize("cuts", [[90], [1] * 90, [2, 2, 31, 1, 1, 40, 13]])
-def test_mlstm_scan_portions_and_dirty_slots(dims, cuts):
+@pytest.mark.parametrize("cuts", [[90], [1] * 90, [2, 2, 31, 1, 1, 40, 13], [70, 20]])
+@pytest.mark.parametrize("blocked", [False, True])
+def test_mlstm_portions_and_dirty_slots(dims, cuts, blocked):
+    """Token by token (blocked=False) and 64 positions at a time (blocked=True: portions longer and shorter than a
+    block, a block that ends inside a portion) against the oracle's loop."""
     from dli_b200 import ops
 
     H, D, V = dims
@@ -299,7 +302,7 @@ def test_mlstm_scan_portions_and_dirty_slots(dims, cuts):
         o = torch.empty(c, H * V, device=DEV)
         ops.mlstm_ragged(pr, torch.empty(c * H * V, device=DEV), o, ent, H, D, V, 0, H * D, 2 * H * D,
                          2 * H * D + 2 * H * V, 2 * H * D + 2 * H * V + H, 2 * H * D + H * V, ib.to(DEV), fb.to(DEV),
-                         6.0, nw.to(DEV), 1e-5, S, n, mm)
+                         6.0, nw.to(DEV), 1e-5, S, n, mm, blocked=blocked)
         out[at:at + c] = o
         at += c
     assert at == T
