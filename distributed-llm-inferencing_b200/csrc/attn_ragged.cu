@@ -114,6 +114,34 @@ struct AttnRun {
   const float* sin_v;
 };
 
+// q (shared, fp32) . k row (global): 16-byte loads where the row allows them
+__device__ __forceinline__ float dot_row(const float* q, const bf16* kr, int D) {
+  float d = 0.f;
+  if (D % 8 == 0 && (reinterpret_cast<uintptr_t>(kr) & 15u) == 0) {
+    for (int c = 0; c < D; c += 8) {
+      float f[8];
+      unpack8(ld_16B(kr + c), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d = fmaf(q[c + j], f[j], d);
+    }
+  } else {
+    for (int c = 0; c < D; ++c) d = fmaf(q[c], __bfloat162float(kr[c]), d);
+  }
+  return d;
+}
+__device__ __forceinline__ float dot_row(const float* q, const float* kr, int D) {
+  float d = 0.f;
+  if (D % 4 == 0 && (reinterpret_cast<uintptr_t>(kr) & 15u) == 0) {
+    for (int c = 0; c < D; c += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(kr + c);
+      d = fmaf(q[c], f.x, d); d = fmaf(q[c + 1], f.y, d); d = fmaf(q[c + 2], f.z, d); d = fmaf(q[c + 3], f.w, d);
+    }
+  } else {
+    for (int c = 0; c < D; ++c) d = fmaf(q[c], kr[c], d);
+  }
+  return d;
+}
+
 constexpr int kAttnThreads = 128;
 constexpr int kAttnMaxVPerThread = 4;  // V <= 512
 
@@ -154,9 +182,7 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     float s = -INFINITY;
     if (j <= pos) {
       const E* kr = kc + (((size_t)pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size) * a.D;
-      float d = 0.f;
-      for (int c = 0; c < a.D; ++c) d = fmaf(q[c], a_to_f(kr[c]), d);
-      s = d;
+      s = dot_row(q, kr, a.D);
     }
     // block maximum
     float mx = warp_max(s);

@@ -163,15 +163,36 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
     const int len = min(kMcL, e.z - t0);
     const E* base = proj + (size_t)(e.y + t0) * a.ldp;
     // q, k transposed (zero beyond len), v slice, gates
-    for (int i = tid; i < kMcL * D; i += kMcThreads) {
-      const int t = i / D, d = i - t * D;
-      float qv = 0.f, kv = 0.f;
-      if (t < len) {
-        qv = m_to_f(base[(size_t)t * a.ldp + a.q_off + h * D + d]) * qscale;
-        kv = m_to_f(base[(size_t)t * a.ldp + a.k_off + h * D + d]);
+    if (sizeof(E) == 2 && D % 8 == 0 && (a.q_off + h * D) % 8 == 0 && (a.k_off + h * D) % 8 == 0 && a.ldp % 8 == 0) {
+      // 16-byte loads; consecutive threads take consecutive rows so that the transposed stores do not collide
+#pragma unroll 4
+      for (int i = tid; i < kMcL * (D / 8); i += kMcThreads) {
+        const int t = i % kMcL, d8 = i / kMcL;
+        uint4 uq = make_uint4(0, 0, 0, 0), uk = uq;
+        if (t < len) {
+          uq = ld_16B(base + (size_t)t * a.ldp + a.q_off + h * D + d8 * 8);
+          uk = ld_16B(base + (size_t)t * a.ldp + a.k_off + h * D + d8 * 8);
+        }
+        float fq[8], fk[8];
+        unpack8(uq, fq);
+        unpack8(uk, fk);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          qT[(d8 * 8 + j) * kMcLp + t] = fq[j] * qscale;
+          kT[(d8 * 8 + j) * kMcLp + t] = fk[j];
+        }
       }
-      qT[d * kMcLp + t] = qv;
-      kT[d * kMcLp + t] = kv;
+    } else {
+      for (int i = tid; i < kMcL * D; i += kMcThreads) {
+        const int t = i / D, d = i - t * D;
+        float qv = 0.f, kv = 0.f;
+        if (t < len) {
+          qv = m_to_f(base[(size_t)t * a.ldp + a.q_off + h * D + d]) * qscale;
+          kv = m_to_f(base[(size_t)t * a.ldp + a.k_off + h * D + d]);
+        }
+        qT[d * kMcLp + t] = qv;
+        kT[d * kMcLp + t] = kv;
+      }
     }
     for (int i = tid; i < kMcL * kMcCols; i += kMcThreads) {
       const int t = i / kMcCols, c = c0 + i % kMcCols;

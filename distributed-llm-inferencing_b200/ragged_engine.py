@@ -138,6 +138,8 @@ class RaggedEngine:
         self._tables: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._ws_rows = 0
         self._meta_cap = 0
+        self._graphs: Dict[tuple, object] = {}
+        self.use_cuda_graph = os.environ.get("DLI_RAGGED_GRAPH", "1") == "1"
         self.eos_token_ids: tuple = ()
         self.pad_token_id: Optional[int] = None
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
@@ -215,6 +217,7 @@ class RaggedEngine:
         return total
 
     def unload(self) -> None:
+        self._graphs.clear()
         self.w.clear()
         self.layers.clear()
         self.kv.release_all()
@@ -259,7 +262,9 @@ class RaggedEngine:
         self._y = torch.empty(rows, s.width, dtype=E, device=dev)
         self._act = torch.empty(rows * max(ff, 1), dtype=E, device=dev)
         self._gu = torch.empty(rows * max(2 * ff, 1), dtype=E, device=dev)
+        self._hw = torch.empty(max(self.max_batch, 8), s.width, dtype=E, device=dev)
         self._ws_rows = rows
+        self._graphs.clear()  # captured graphs hold the old workspace pointers
 
     def _lin(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = x @ w.T: the framework's bf16 projection (tcgen05 GEMM / weight-streaming GEMV) where its alignment
@@ -313,9 +318,16 @@ class RaggedEngine:
         total = 2 * r4 + e4 + w4 + len(tiles)
         if total > self._meta_cap:
             self._meta_cap = _ceil(total, 1024)
-            self._meta_host = torch.zeros(self._meta_cap, dtype=torch.int32).pin_memory()
+            # a ring of pinned staging buffers: the host may run ahead of the device by several steps, and a buffer
+            # is written again only after the copy that read it has finished
+            self._meta_ring = [(torch.zeros(self._meta_cap, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+                               for _ in range(4)]
+            self._meta_turn = 0
             self._meta_dev = torch.zeros(self._meta_cap, dtype=torch.int32, device=dev)
-        mh = self._meta_host
+            self._graphs.clear()  # captured graphs hold the old buffer's addresses
+        self._meta_turn = (self._meta_turn + 1) % len(self._meta_ring)
+        mh, copied = self._meta_ring[self._meta_turn]
+        copied.synchronize()
         mh[:rows] = torch.tensor(tokens, dtype=torch.int32)
         mh[r4:r4 + rows] = torch.tensor(row_ent, dtype=torch.int32)
         mh[2 * r4:2 * r4 + e4] = torch.tensor(ent, dtype=torch.int32)
@@ -325,12 +337,53 @@ class RaggedEngine:
             mh[2 * r4 + e4 + w4:total] = torch.tensor(tiles, dtype=torch.int32)
         md = self._meta_dev
         md[:total].copy_(mh[:total], non_blocking=True)
+        copied.record()
         d_tok, d_rent, d_ent = md[:rows], md[r4:r4 + rows], md[2 * r4:2 * r4 + e4]
         d_want = md[2 * r4 + e4:2 * r4 + e4 + len(want_rows)]
         d_tiles = md[2 * r4 + e4 + w4:total]
 
         self._workspace(rows)
         long_step = any(len(t) >= self.tc_min_rows for _, t in batch)  # a portion of a prompt is in the step
+        nw = len(want_rows)
+        views = (d_tok, d_rent, d_ent, d_want, d_tiles)
+        # a step of single tokens (decode) has the same launches every time: the device buffers of its description sit
+        # at fixed addresses per batch size, so it is captured once as a CUDA graph and replayed
+        if self.use_cuda_graph and rows == n_ent and self.layer_trace is None:
+            logits = self._graphed_forward(rows, n_ent, nw, views)
+        else:
+            logits = self._forward(rows, n_ent, nw, views, long_step, bool(tiles), None)
+        for slot, toks in batch:
+            self.lengths[slot] += len(toks)
+        if logits is None:
+            return torch.empty(0, s.vocab, dtype=E, device=dev)
+        return logits[:, :s.vocab]
+
+    def _graphed_forward(self, rows, n_ent, nw, views):
+        key = (rows, nw)
+        hit = self._graphs.get(key)
+        if hit is None:
+            # first use: run it (this also sets every kernel's attributes); the capture happens at the second use,
+            # because a capture does not execute and the step must advance the caches exactly once
+            self._graphs[key] = "warm"
+            return self._forward(rows, n_ent, nw, views, False, False, None)
+        if hit == "warm":
+            out = torch.empty(max(nw, 1), self.w["head"].shape[0], dtype=self.dtype, device=self.device)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                self._forward(rows, n_ent, nw, views, False, False, out)
+            self._graphs[key] = hit = (g, out, ops.launch_count - n0)
+        g, out, launches = hit
+        g.replay()
+        ops.launch_count += launches
+        return out[:nw].clone() if nw else None
+
+    def _forward(self, rows, n_ent, nw, views, long_step, use_tiles, logits_out):
+        """Every kernel of one step, in order; logits_out: where the logits go (a buffer of fixed address under capture)."""
+        s, dev, E = self.spec, self.device, self.dtype
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        tiles = use_tiles
         W = s.width
         x, hn, hc = self._x[:rows], self._hn[:rows], self._hc[:rows]
         y = self._y[:rows]
@@ -391,17 +444,14 @@ class RaggedEngine:
             ops.postnorm_add_norm(y, x, g_post, s.eps, hn, g_next)
             if self.layer_trace is not None:
                 self.layer_trace.append(x.clone())
-        for slot, toks in batch:
-            self.lengths[slot] += len(toks)
-        nw = len(want_rows)
         if nw == 0:
-            return torch.empty(0, s.vocab, dtype=E, device=dev)
-        hw = torch.empty(nw, W, dtype=E, device=dev)
+            return None
+        hw = self._hw[:nw] if nw <= self._hw.shape[0] else torch.empty(nw, W, dtype=E, device=dev)
         ops.gather_cast(hn, d_want, hw)
         vp = self.w["head"].shape[0]
-        logits = torch.empty(nw, vp, dtype=E, device=dev)
+        logits = logits_out[:nw] if logits_out is not None else torch.empty(nw, vp, dtype=E, device=dev)
         self._lin(hw, self.w["head"], logits)
-        return logits[:, :s.vocab]
+        return logits
 
     def _iota(self, rows: int) -> torch.Tensor:
         if getattr(self, "_iota_t", None) is None or self._iota_t.numel() < rows:

@@ -258,3 +258,29 @@ def test_bfloat16_portions_on_the_tensor_core_attention():
     for got in (whole, parts, rowwise):
         assert rel_err(got, ref).max() < TOL16
     assert rel_err(whole, rowwise.double()).max() < TOL16 / 2
+
+
+def test_decode_steps_replayed_as_a_graph_equal_eager_steps():
+    """Steps of single tokens are captured once per batch size and replayed; the logits equal the eager launches' bit
+    for bit, also when the batch size changes back and forth and a sequence leaves in between."""
+    cfg = cfg_a()
+    outs = []
+    for graph in (True, False):
+        eng, sd = build(cfg, torch.float32, max_batch=3)
+        eng.use_cuda_graph = graph
+        seqs = [prompt(n, cfg["vocab"], 60 + i) for i, n in enumerate((30, 30, 30))]
+        slots = [eng.open_sequence() for _ in seqs]
+        got = [eng.step([(slots[i], seqs[i][:9]) for i in range(3)])]
+        for t in range(9, 20):
+            got.append(eng.step([(slots[i], [seqs[i][t]]) for i in range(3)]))
+        eng.close_sequence(slots[1])
+        for t in range(20, 30):
+            got.append(eng.step([(slots[i], [seqs[i][t]]) for i in (0, 2)]))
+            if t % 3 == 0:
+                got.append(eng.step([(slots[0], [5])]))
+                seqs[0].insert(t + 1, 5)
+                seqs[0].pop()
+        outs.append(torch.cat([g.float().cpu() for g in got]))
+        if graph:
+            assert any(isinstance(v, tuple) for v in eng._graphs.values())
+    assert torch.equal(outs[0], outs[1])
