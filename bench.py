@@ -512,9 +512,11 @@ def hybrid_kernel_times(eng, spec, T, peaks):
     hbm = peaks["hbm_gbs"] * 1e9
     res = {}
 
-    def timeit(fn, n=5):
+    def timeit(fn, n=5, reps=10):
+        """ms per call: `reps` back-to-back launches per event bracket, so that a short kernel is not timed as one
+        launch latency (the convolution and the recurrence advance their state; any state is as good as another)."""
         fn()
-        return statistics.median(ev_time_ms(fn) for _ in range(n))
+        return statistics.median(ev_time_ms(lambda: [fn() for _ in range(reps)]) for _ in range(n)) / reps
 
     for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
         row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
@@ -573,6 +575,35 @@ def hybrid_kernel_times(eng, spec, T, peaks):
             fl = rows * m.heads * m.dim * m.vdim * 4
             res[f"{tag}_mlstm"] = {"ms": round(ms, 4), "state_update_tflops": round(fl / (ms / 1e3) / 1e12, 3)}
     eng.close_sequence(slot)
+    # the like kernels of the uniform stack at the same sizes (bf16 residual, rotate-half RoPE, plain softmax)
+    H, KV, hd = att.heads, att.kv_heads, att.dim
+    if att.dim == att.vdim and hd in (64, 128):
+        qkv = (0.5 * torch.randn(T, (H + 2 * KV) * hd, device=dev)).to(torch.bfloat16)
+        o = torch.empty(T, H * hd, dtype=torch.bfloat16, device=dev)
+        ms = timeit(lambda: ops.attn_prefill(qkv, o, 1, T, H, KV, hd, hd ** -0.5))
+        fl = 2 * (T * T // 2) * H * 2 * hd
+        res["uniform_prefill_attn"] = {"ms": round(ms, 4), "of_bf16_peak": round(fl / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        ms = timeit(lambda: ops.attn_prefill(qkv, o, 1, T, H, KV, hd, hd ** -0.5, tensor_core=False))
+        res["uniform_prefill_attn_mma_sync"] = {"ms": round(ms, 4), "of_bf16_peak": round(fl / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        ps = eng.kv.page_size
+        n_pages = (T + 1 + ps - 1) // ps
+        kc = torch.randn(n_pages, KV, ps, hd, device=dev).to(torch.bfloat16)
+        vc = torch.randn(n_pages, KV, ps, hd, device=dev).to(torch.bfloat16)
+        ptab = torch.arange(n_pages, dtype=torch.int32, device=dev)[None].contiguous()
+        lens = torch.tensor([T + 1], dtype=torch.int32, device=dev)
+        q1 = qkv[:1].contiguous()
+        o1 = torch.empty(1, H * hd, dtype=torch.bfloat16, device=dev)
+        splits = 8
+        scratch = torch.empty(max(ops.attn_decode_scratch_bytes(1, H, hd, splits) // 4, 1), dtype=torch.float32, device=dev)
+        ms = timeit(lambda: ops.paged_attn_decode(q1, q1.stride(0), kc, vc, ptab, lens, o1, H, KV, hd, hd ** -0.5,
+                                                  num_splits=splits, scratch=scratch))
+        byt = (T + 1) * KV * 2 * hd * 2
+        res["uniform_decode_attn"] = {"ms": round(ms, 4), "of_hbm": round(byt / (ms / 1e3) / hbm, 3)}
+    xb = torch.randn(T, W, device=dev).to(torch.bfloat16)
+    wb = torch.ones(W, dtype=torch.bfloat16, device=dev)
+    ob = torch.empty_like(xb)
+    ms = timeit(lambda: ops.add_rmsnorm(xb, wb, 1e-6, residual=xb, resid_out=ob, out=ob))
+    res["uniform_prefill_add_rmsnorm"] = {"ms": round(ms, 4), "of_hbm": round(T * W * 2 * 4 / (ms / 1e3) / hbm, 3)}
     return res
 
 

@@ -288,23 +288,25 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
     }
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + swz<RBK>(row, c)), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w));
   }
+  // two threads per key row: one page lookup per row and tile, then that row's 16-byte pieces
+  const int lrow = tid >> 1, lhalf = tid & 1;
   auto load_tile = [&](int tile, int stage) {
     const uint32_t dK = sK + stage * kKBytes, dV = sV + stage * kVBytes;
-    for (int id = tid; id < kRtTile * CHK; id += kRtThreads) {
-      const int row = id / CHK, c = id - row * CHK;
-      const int tok = tile * kRtTile + row;
-      const bool valid = tok <= p_last;
-      size_t off = 0;
-      if (valid) off = (((size_t)pt[tok / a.page_size] * a.G + g) * a.page_size + tok % a.page_size) * DK + c * 8;
-      cp_async_16B(dK + swz<RBK>(row, c), kc + off, valid ? 16 : 0);
+    const int tok = tile * kRtTile + lrow;
+    const bool valid = tok <= p_last;
+    size_t rowbase = 0;
+    if (valid) rowbase = ((size_t)pt[tok / a.page_size] * a.G + g) * a.page_size + tok % a.page_size;
+    const bf16* ksrc = kc + rowbase * DK;
+    const bf16* vsrc = vc + rowbase * DV;
+#pragma unroll
+    for (int i = 0; i < CHK / 2; ++i) {
+      const int c = lhalf * (CHK / 2) + i;
+      cp_async_16B(dK + swz<RBK>(lrow, c), ksrc + c * 8, valid ? 16 : 0);
     }
-    for (int id = tid; id < kRtTile * CHV; id += kRtThreads) {
-      const int row = id / CHV, c = id - row * CHV;
-      const int tok = tile * kRtTile + row;
-      const bool valid = tok <= p_last;
-      size_t off = 0;
-      if (valid) off = (((size_t)pt[tok / a.page_size] * a.G + g) * a.page_size + tok % a.page_size) * DV + c * 8;
-      cp_async_16B(dV + swz<RBV>(row, c), vc + off, valid ? 16 : 0);
+#pragma unroll
+    for (int i = 0; i < CHV / 2; ++i) {
+      const int c = lhalf * (CHV / 2) + i;
+      cp_async_16B(dV + swz<RBV>(lrow, c), vsrc + c * 8, valid ? 16 : 0);
     }
   };
   auto row_lo = [&](int pos) {
@@ -382,13 +384,13 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m_run[r], mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = (m_run[r] == -INFINITY) ? 0.f : exp2f((m_run[r] - m_use) * scale_log2);
+      const float corr = (m_run[r] == -INFINITY) ? 0.f : ex2_ftz((m_run[r] - m_use) * scale_log2);
       m_run[r] = m_new;
       float rs = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float p0w = exp2f((s[j][2 * r] - m_use) * scale_log2);
-        const float p1w = exp2f((s[j][2 * r + 1] - m_use) * scale_log2);
+        const float p0w = ex2_ftz((s[j][2 * r] - m_use) * scale_log2);
+        const float p1w = ex2_ftz((s[j][2 * r + 1] - m_use) * scale_log2);
         rs += p0w + p1w;
         pa[j >> 1][(j & 1) * 2 + r] = pack_bf16(p0w, p1w);
       }

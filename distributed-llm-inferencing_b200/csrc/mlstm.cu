@@ -140,6 +140,7 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
   float* Mv = av + kMcL;                    // [L] M_t
   float* bv = Mv + kMcL;                    // [L] b_t
   float* qn = bv + kMcL;                    // [L] n . q per row
+  float* us = qn + kMcL;                    // [L] e^{a_s - M_L}
   pdl_wait();
   pdl_trigger();
   const int4 e = reinterpret_cast<const int4*>(a.ent)[blockIdx.x];
@@ -208,19 +209,34 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
       bv[tid] = fg;   // for now: f_s
     }
     __syncthreads();
-    if (tid == 0) {  // 64 steps: running sums and maxima in order
-      float b = 0.f, M = m0;
-      for (int t = 0; t < kMcL; ++t) {
-        b += bv[t];
-        const float as = av[t] - b;
-        M = fmaxf(M, as);
-        bv[t] = b; av[t] = as; Mv[t] = M;
+    if (tid < 32) {  // running sums and maxima over the block: two positions per lane, warp scans between the lanes
+      const float f0 = bv[2 * tid], f1 = bv[2 * tid + 1];
+      float run = f0 + f1;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, run, o);
+        if (tid >= o) run += up;
       }
+      const float b1 = run, b0 = run - f1;           // inclusive sums at 2*lane and 2*lane + 1
+      const float a0 = av[2 * tid] - b0, a1 = av[2 * tid + 1] - b1;
+      float mx = fmaxf(a0, a1);
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, mx, o);
+        if (tid >= o) mx = fmaxf(mx, up);
+      }
+      const float before = __shfl_up_sync(0xffffffffu, mx, 1);
+      const float M0 = fmaxf(m0, fmaxf(tid > 0 ? before : -INFINITY, a0));
+      bv[2 * tid] = b0; bv[2 * tid + 1] = b1;
+      av[2 * tid] = a0; av[2 * tid + 1] = a1;
+      Mv[2 * tid] = M0; Mv[2 * tid + 1] = fmaxf(M0, a1);
     }
     __syncthreads();
+    if (tid < kMcL) us[tid] = expf(av[tid] - Mv[kMcL - 1]);  // weights of the block's inputs in the state at its end
     // AT[s][t] = (q_t . k_s) e^{a_s - M_t} for s <= t, else 0: rows t = 4ty.., columns s = 4tx..
     {
       float acc[4][4] = {};
+#pragma unroll 4
       for (int d = 0; d < D; ++d) {
         const float4 qa = *reinterpret_cast<const float4*>(qT + d * kMcLp + 4 * ty);
         const float4 kb = *reinterpret_cast<const float4*>(kT + d * kMcLp + 4 * tx);
@@ -240,14 +256,20 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
     }
     // n . q of the incoming state, per row
     if (tid < kMcL) {
-      float d0 = 0.f;
-      for (int d = 0; d < D; ++d) d0 = fmaf(ns[d], qT[d * kMcLp + tid], d0);
-      qn[tid] = d0;
+      float d0 = 0.f, d1 = 0.f;
+      int d = 0;
+      for (; d + 1 < D; d += 2) {
+        d0 = fmaf(ns[d], qT[d * kMcLp + tid], d0);
+        d1 = fmaf(ns[d + 1], qT[(d + 1) * kMcLp + tid], d1);
+      }
+      if (d < D) d0 = fmaf(ns[d], qT[d * kMcLp + tid], d0);
+      qn[tid] = d0 + d1;
     }
     __syncthreads();
     // read-out: rows t = 4ty.., columns c = 4tx..
     {
       float inter[4][4] = {}, intra[4][4] = {};
+#pragma unroll 4
       for (int d = 0; d < D; ++d) {
         const float4 qa = *reinterpret_cast<const float4*>(qT + d * kMcLp + 4 * ty);
         const float4 sb = *reinterpret_cast<const float4*>(Ss + d * kMcCols + 4 * tx);
@@ -258,6 +280,7 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
           for (int j = 0; j < 4; ++j) inter[i][j] = fmaf(qv[i], sv[j], inter[i][j]);
       }
       float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
       for (int sidx = 0; sidx < len; ++sidx) {
         const float4 aa = *reinterpret_cast<const float4*>(AT + sidx * kMcLp + 4 * ty);
         const float4 vb = *reinterpret_cast<const float4*>(vs + sidx * kMcCols + 4 * tx);
@@ -286,21 +309,33 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
     // the state moves to the end of the block
     {
       const float ML = Mv[kMcL - 1], gL = expf(m0 - ML);
-      for (int d = ty; d < D; d += 16) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        float nacc = 0.f;
+      // 8 rows x 4 columns per thread and pass: one value row and one weight per position serve 32 FMAs
+      for (int dbase = 0; dbase < D; dbase += 128) {
+        float acc[8][4] = {};
+        float nacc[8] = {};
         for (int sidx = 0; sidx < len; ++sidx) {
-          const float u = expf(av[sidx] - ML) * kT[d * kMcLp + sidx];
+          const float u = us[sidx];
           const float4 vb = *reinterpret_cast<const float4*>(vs + sidx * kMcCols + 4 * tx);
-          acc[0] = fmaf(u, vb.x, acc[0]); acc[1] = fmaf(u, vb.y, acc[1]);
-          acc[2] = fmaf(u, vb.z, acc[2]); acc[3] = fmaf(u, vb.w, acc[3]);
-          nacc += u;
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int d = dbase + ty + 16 * r;
+            const float uk = d < D ? u * kT[d * kMcLp + sidx] : 0.f;
+            acc[r][0] = fmaf(uk, vb.x, acc[r][0]); acc[r][1] = fmaf(uk, vb.y, acc[r][1]);
+            acc[r][2] = fmaf(uk, vb.z, acc[r][2]); acc[r][3] = fmaf(uk, vb.w, acc[r][3]);
+            nacc[r] += uk;
+          }
         }
-        float4* sp = reinterpret_cast<float4*>(Ss + d * kMcCols + 4 * tx);
-        float4 sv = *sp;
-        sv.x = gL * sv.x + acc[0]; sv.y = gL * sv.y + acc[1]; sv.z = gL * sv.z + acc[2]; sv.w = gL * sv.w + acc[3];
-        *sp = sv;
-        if (tx == 0) ns[d] = gL * ns[d] + nacc;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int d = dbase + ty + 16 * r;
+          if (d >= D) continue;
+          float4* sp = reinterpret_cast<float4*>(Ss + d * kMcCols + 4 * tx);
+          float4 sv = *sp;
+          sv.x = gL * sv.x + acc[r][0]; sv.y = gL * sv.y + acc[r][1];
+          sv.z = gL * sv.z + acc[r][2]; sv.w = gL * sv.w + acc[r][3];
+          *sp = sv;
+          if (tx == 0) ns[d] = gL * ns[d] + nacc[r];
+        }
       }
       m0 = bv[kMcL - 1] + ML;
     }
@@ -317,7 +352,7 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
 }
 
 static size_t mlstm_chunk_smem(int D) {
-  return sizeof(float) * (2 * (size_t)D * kMcLp + (size_t)D * kMcCols + kMcL * kMcLp + kMcL * kMcCols + D + 4 * kMcL);
+  return sizeof(float) * (2 * (size_t)D * kMcLp + (size_t)D * kMcCols + kMcL * kMcLp + kMcL * kMcCols + D + 5 * kMcL);
 }
 
 // y[row, h, :] = o / rms(o over the head) * w[h, :] * sigmoid(gate[row, h, :]); one warp per (row, head).

@@ -113,6 +113,31 @@ causal_conv_kernel(const float* __restrict__ h, const float* __restrict__ tail, 
   }
 }
 
+// The same for a step in which every entry brings ONE row (decode): the row's CTA is the only reader and writer of
+// its slot's tail, so the convolution and the tail's shift are one kernel.
+template <typename E>
+__global__ void __launch_bounds__(256)
+causal_conv_single_kernel(const float* __restrict__ h, float* __restrict__ tail, const float* __restrict__ w,
+                          const int32_t* __restrict__ ent, E* __restrict__ out, int d, int taps) {
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  const int4 e = reinterpret_cast<const int4*>(ent)[row];  // slot, row0 (== row), 1, position
+  const int keep = taps - 1;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float* t = tail + (size_t)e.x * keep * d + c;
+    const float cur = h[(size_t)row * d + c];
+    float acc = w[(size_t)c * taps + keep] * cur;
+    for (int i = 0; i < keep; ++i) {  // tail slot i holds position pos - keep + i
+      const float v = (e.w - keep + i >= 0) ? t[(size_t)i * d] : 0.f;
+      acc += w[(size_t)c * taps + i] * v;
+      if (i > 0) t[(size_t)(i - 1) * d] = v;
+    }
+    if (keep > 0) t[(size_t)(keep - 1) * d] = cur;
+    out[(size_t)row * d + c] = from_f<E>(cur + acc);
+  }
+}
+
 // After the convolution of a step: the tail of every entry's slot becomes the last taps - 1 inputs of the sequence.
 __global__ void __launch_bounds__(256)
 conv_tail_update_kernel(const float* __restrict__ h, float* __restrict__ tail, const int32_t* __restrict__ ent, int d,
@@ -244,6 +269,11 @@ int dli_causal_conv_ragged(const float* h, float* tail, const float* w, const in
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == n_ent && taps > 1) {  // one row per entry
+    if (dt == 0) DLI_LAUNCH("causal_conv_single", causal_conv_single_kernel<bf16>, dim3(rows), dim3(256), 0, s, h, tail, w, ent, (bf16*)out, d, taps);
+    else DLI_LAUNCH("causal_conv_single", causal_conv_single_kernel<float>, dim3(rows), dim3(256), 0, s, h, tail, w, ent, (float*)out, d, taps);
+    return DLI_OK;
+  }
   if (dt == 0) DLI_LAUNCH("causal_conv", causal_conv_kernel<bf16>, dim3(rows), dim3(256), 0, s, h, (const float*)tail, w, row_ent, ent, (bf16*)out, d, taps);
   else DLI_LAUNCH("causal_conv", causal_conv_kernel<float>, dim3(rows), dim3(256), 0, s, h, (const float*)tail, w, row_ent, ent, (float*)out, d, taps);
   if (taps > 1) DLI_LAUNCH("conv_tail_update", conv_tail_update_kernel, dim3(n_ent), dim3(256), 0, s, h, tail, ent, d, taps);

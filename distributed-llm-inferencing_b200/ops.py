@@ -494,7 +494,8 @@ def causal_conv_ragged(h, tail, w, row_ent, ent, out):
     """out = h + conv(h) over time per channel (w float32 [d, taps]); tail float32 [slots, taps-1, d] is advanced."""
     _f32(h, tail, w), _i32(row_ent, ent), _req(out, out.dtype)
     taps = w.shape[1]
-    _call("dli_causal_conv_ragged", 2 if taps > 1 else 1, _p(h), _p(tail), _p(w), _p(row_ent), _p(ent), _p(out),
+    single = h.shape[0] == ent.numel() // 4  # one row per entry: convolution and tail shift are one kernel
+    _call("dli_causal_conv_ragged", 2 if (taps > 1 and not single) else 1, _p(h), _p(tail), _p(w), _p(row_ent), _p(ent), _p(out),
           h.shape[0], ent.numel() // 4, h.shape[1], taps, _dt(out), _stream())
     return out
 
