@@ -564,6 +564,15 @@ def hybrid_kernel_times(eng, spec, T, peaks):
         mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
         oscr = torch.empty(rows * m.heads * m.vdim, device=dev)
         off = P["off"]
+        if rows > 64:
+            rtiles = torch.tensor([[0, q0] for q0 in range(0, rows, 64)], dtype=torch.int32, device=dev)
+            scr = torch.empty(ops.mlstm_parallel_scratch_floats(rtiles.shape[0], m.heads, m.dim, m.vdim), device=dev)
+            ms = timeit(lambda: ops.mlstm_ragged_parallel(proj, oscr, mix, ent, rtiles, scr, m.heads, m.dim, m.vdim, off["q"],
+                                                          off["k"], off["v"], off["i"], off["f"], off["g"], P["i_b"],
+                                                          P["f_b"], m.gate_cap, P["out_norm"], 1e-6, eng.slots[("S", li_r)],
+                                                          eng.slots[("n", li_r)], eng.slots[("m", li_r)]))
+            fl = rows * m.heads * (m.dim * m.vdim * 4 + 64 * (m.dim + m.vdim))  # state move + read-out, FMAs counted as 2
+            res[f"{tag}_mlstm_blocks_parallel"] = {"ms": round(ms, 4), "tflops_fp32": round(fl / (ms / 1e3) / 1e12, 3)}
         ms = timeit(lambda: ops.mlstm_ragged(proj, oscr, mix, ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"],
                                              off["i"], off["f"], off["g"], P["i_b"], P["f_b"], m.gate_cap, P["out_norm"],
                                              1e-6, eng.slots[("S", li_r)], eng.slots[("n", li_r)], eng.slots[("m", li_r)],

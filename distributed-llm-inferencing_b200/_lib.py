@@ -82,6 +82,9 @@ SIGNATURES = {
     "dli_attn_ragged_tc_supported": (_i, [_i, _i, _i]),
     "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
                                 _i, _vp, _vp, _vp]),
+    "dli_mlstm_parallel_scratch_floats": (_sz, [_i, _i, _i, _i]),
+    "dli_mlstm_ragged_parallel": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                       _vp, _vp, _f, _vp, _f, _vp, _vp, _vp, _i, _vp]),
     "dli_mlstm_ragged": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp,
                               _f, _vp, _vp, _vp, _i, _i, _vp]),
 }

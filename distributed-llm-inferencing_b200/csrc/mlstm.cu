@@ -351,6 +351,298 @@ mlstm_chunk_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs 
   }
 }
 
+// ---- long portions: the blocks of one sequence in parallel ------------------------------------------------------
+// The block form above walks a sequence's blocks in order inside one CTA, which leaves most SMs idle for a single long
+// prompt.  Here every 64-position block gets its own CTAs, in three passes over tiles[2c] = entry, tiles[2c+1] = first
+// row of block c within the entry (the blocks of an entry are consecutive):
+//   pass 1 (parallel):  what block c adds to the state, as if it started from nothing: with A_c = max_s a_s,
+//                       U_c = sum_s e^{a_s - A_c} k_s v_s^T, nU_c likewise, and the scalars (b_L, A_c);
+//   pass 2 (in order, elementwise): S_in(c) is stored where U_c was, then S <- e^{m_0 - M} S + e^{A_c - M} U_c with
+//                       M = max(m_0, A_c), m_0 <- b_L + M; the sequence's slot gets the final state;
+//   pass 3 (parallel):  the read-outs of block c from (S_in(c), n_in(c), m_0(c)) as in the block form.
+struct MlstmPar {
+  const int32_t* tiles;
+  float* cS;   // [blocks, H, D, V]
+  float* cn;   // [blocks, H, D]
+  float* csc;  // [blocks, H, 4] = (b_L, A_c, m_0 of the block, -)
+};
+
+template <typename E>
+__device__ __forceinline__ void mlstm_load_kv_gates(const E* base, const MlstmArgs& a, int h, int len, int c0, float qscale,
+                                                    float ib, float fb, float* qT, float* kT, float* vs, float* av,
+                                                    float* bv, bool want_q) {
+  const int D = a.D, tid = threadIdx.x;
+  if (sizeof(E) == 2 && D % 8 == 0 && (a.q_off + h * D) % 8 == 0 && (a.k_off + h * D) % 8 == 0 && a.ldp % 8 == 0) {
+#pragma unroll 4
+    for (int i = tid; i < kMcL * (D / 8); i += kMcThreads) {
+      const int t = i % kMcL, d8 = i / kMcL;
+      uint4 uq = make_uint4(0, 0, 0, 0), uk = uq;
+      if (t < len) {
+        if (want_q) uq = ld_16B(base + (size_t)t * a.ldp + a.q_off + h * D + d8 * 8);
+        uk = ld_16B(base + (size_t)t * a.ldp + a.k_off + h * D + d8 * 8);
+      }
+      float fq[8], fk[8];
+      unpack8(uq, fq);
+      unpack8(uk, fk);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (want_q) qT[(d8 * 8 + j) * kMcLp + t] = fq[j] * qscale;
+        kT[(d8 * 8 + j) * kMcLp + t] = fk[j];
+      }
+    }
+  } else {
+    for (int i = tid; i < kMcL * D; i += kMcThreads) {
+      const int t = i / D, d = i - t * D;
+      float qv = 0.f, kv = 0.f;
+      if (t < len) {
+        if (want_q) qv = m_to_f(base[(size_t)t * a.ldp + a.q_off + h * D + d]) * qscale;
+        kv = m_to_f(base[(size_t)t * a.ldp + a.k_off + h * D + d]);
+      }
+      if (want_q) qT[d * kMcLp + t] = qv;
+      kT[d * kMcLp + t] = kv;
+    }
+  }
+  for (int i = tid; i < kMcL * kMcCols; i += kMcThreads) {
+    const int t = i / kMcCols, c = c0 + i % kMcCols;
+    vs[i] = (t < len && c < a.V) ? m_to_f(base[(size_t)t * a.ldp + a.v_off + h * a.V + c]) : 0.f;
+  }
+  if (tid < kMcL) {
+    float ig = -INFINITY, fg = 0.f;
+    if (tid < len) {
+      ig = soft_cap(m_to_f(base[(size_t)tid * a.ldp + a.i_off + h]) + ib, a.cap);
+      fg = log_sigmoid(soft_cap(m_to_f(base[(size_t)tid * a.ldp + a.f_off + h]) + fb, a.cap));
+    }
+    av[tid] = ig;
+    bv[tid] = fg;
+  }
+}
+
+// Warp 0: b_t (running sum of the log forget gates), a_s = i_s - b_s and M_t = max(m_start, max_{s<=t} a_s).
+__device__ __forceinline__ void mlstm_block_scan(float m_start, float* av, float* bv, float* Mv) {
+  const int tid = threadIdx.x;
+  if (tid < 32) {
+    const float f0 = bv[2 * tid], f1 = bv[2 * tid + 1];
+    float run = f0 + f1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, run, o);
+      if (tid >= o) run += up;
+    }
+    const float b1 = run, b0 = run - f1;
+    const float a0 = av[2 * tid] - b0, a1 = av[2 * tid + 1] - b1;
+    float mx = fmaxf(a0, a1);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, mx, o);
+      if (tid >= o) mx = fmaxf(mx, up);
+    }
+    const float before = __shfl_up_sync(0xffffffffu, mx, 1);
+    const float M0 = fmaxf(m_start, fmaxf(tid > 0 ? before : -INFINITY, a0));
+    bv[2 * tid] = b0; bv[2 * tid + 1] = b1;
+    av[2 * tid] = a0; av[2 * tid + 1] = a1;
+    Mv[2 * tid] = M0; Mv[2 * tid + 1] = fmaxf(M0, a1);
+  }
+}
+
+template <typename E>
+__global__ void __launch_bounds__(kMcThreads)
+mlstm_par_local_kernel(const E* __restrict__ proj, MlstmArgs a, MlstmPar p) {
+  extern __shared__ __align__(16) float smc[];
+  const int D = a.D;
+  float* kT = smc;                          // [D][kMcLp]
+  float* vs = kT + (size_t)D * kMcLp;       // [L][kMcCols]
+  float* av = vs + kMcL * kMcCols;
+  float* Mv = av + kMcL;
+  float* bv = Mv + kMcL;
+  float* us = bv + kMcL;
+  pdl_wait();
+  pdl_trigger();
+  const int blk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kMcCols;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[p.tiles[2 * blk]];
+  const int t0 = p.tiles[2 * blk + 1], len = min(kMcL, e.z - t0);
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const float ib = a.i_bias ? a.i_bias[h] : 0.f, fb = a.f_bias ? a.f_bias[h] : 0.f;
+  mlstm_load_kv_gates(proj + (size_t)(e.y + t0) * a.ldp, a, h, len, c0, 1.f, ib, fb, (float*)nullptr, kT, vs, av, bv, false);
+  __syncthreads();
+  mlstm_block_scan(-INFINITY, av, bv, Mv);
+  __syncthreads();
+  const float A = Mv[kMcL - 1];
+  if (tid < kMcL) us[tid] = expf(av[tid] - A);
+  __syncthreads();
+  float* Ug = p.cS + ((size_t)blk * a.H + h) * D * a.V;
+  float* nUg = p.cn + ((size_t)blk * a.H + h) * D;
+  for (int dbase = 0; dbase < D; dbase += 128) {
+    float acc[8][4] = {};
+    float nacc[8] = {};
+    for (int sidx = 0; sidx < len; ++sidx) {
+      const float u = us[sidx];
+      const float4 vb = *reinterpret_cast<const float4*>(vs + sidx * kMcCols + 4 * tx);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int d = dbase + ty + 16 * r;
+        const float uk = d < D ? u * kT[d * kMcLp + sidx] : 0.f;
+        acc[r][0] = fmaf(uk, vb.x, acc[r][0]); acc[r][1] = fmaf(uk, vb.y, acc[r][1]);
+        acc[r][2] = fmaf(uk, vb.z, acc[r][2]); acc[r][3] = fmaf(uk, vb.w, acc[r][3]);
+        nacc[r] += uk;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int d = dbase + ty + 16 * r;
+      if (d >= D) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + 4 * tx + j;
+        if (c < a.V) Ug[(size_t)d * a.V + c] = acc[r][j];
+      }
+      if (tx == 0 && blockIdx.z == 0) nUg[d] = nacc[r];
+    }
+  }
+  if (tid == 0 && blockIdx.z == 0) {
+    float* sc = p.csc + ((size_t)blk * a.H + h) * 4;
+    sc[0] = bv[kMcL - 1];
+    sc[1] = A;
+  }
+}
+
+// pass 2: one thread per state element (the D*V entries of S, then the D entries of n), blocks of the entry in order
+__global__ void __launch_bounds__(256)
+mlstm_par_carry_kernel(MlstmArgs a, MlstmPar p, int n_tiles) {
+  pdl_wait();
+  pdl_trigger();
+  const int ent_i = blockIdx.x, h = blockIdx.y;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[ent_i];
+  const size_t DV = (size_t)a.D * a.V, total = DV + a.D;
+  const size_t idx = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
+  int first = 0;
+  while (first < n_tiles && p.tiles[2 * first] != ent_i) ++first;
+  const int nblk = (e.z + kMcL - 1) / kMcL;
+  const bool fresh = e.w == 0;
+  float* mg = a.m + (size_t)e.x * a.H + h;
+  float m0 = fresh ? 0.f : *mg;
+  float* state = nullptr;
+  if (idx < DV) state = a.S + ((size_t)e.x * a.H + h) * DV + idx;
+  else if (idx < total) state = a.n + ((size_t)e.x * a.H + h) * a.D + (idx - DV);
+  float sv = (state && !fresh) ? *state : 0.f;
+  for (int b = 0; b < nblk; ++b) {
+    const int blk = first + b;
+    float* sc = p.csc + ((size_t)blk * a.H + h) * 4;
+    const float bL = sc[0], A = sc[1];
+    const float M = fmaxf(m0, A), g = expf(m0 - M), w = expf(A - M);
+    if (state) {
+      float* slot = idx < DV ? p.cS + ((size_t)blk * a.H + h) * DV + idx : p.cn + ((size_t)blk * a.H + h) * a.D + (idx - DV);
+      const float u = *slot;
+      *slot = sv;
+      sv = g * sv + w * u;
+    }
+    if (idx == 0) sc[2] = m0;
+    m0 = bL + M;
+  }
+  if (state) *state = sv;
+  // the slot's m is read by every CTA of this pass: its new value waits in the last block's scalars until pass 3
+  if (idx == 0) p.csc[((size_t)(first + nblk - 1) * a.H + h) * 4 + 3] = m0;
+}
+
+template <typename E>
+__global__ void __launch_bounds__(kMcThreads)
+mlstm_par_readout_kernel(const E* __restrict__ proj, float* __restrict__ o, MlstmArgs a, MlstmPar p) {
+  extern __shared__ __align__(16) float smc[];
+  const int D = a.D;
+  float* qT = smc;
+  float* kT = qT + (size_t)D * kMcLp;
+  float* Ss = kT + (size_t)D * kMcLp;
+  float* AT = Ss + (size_t)D * kMcCols;
+  float* vs = AT + kMcL * kMcLp;
+  float* ns = vs + kMcL * kMcCols;
+  float* av = ns + D;
+  float* Mv = av + kMcL;
+  float* bv = Mv + kMcL;
+  float* qn = bv + kMcL;
+  pdl_wait();
+  pdl_trigger();
+  const int blk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kMcCols;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[p.tiles[2 * blk]];
+  const int t0 = p.tiles[2 * blk + 1], len = min(kMcL, e.z - t0);
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const float ib = a.i_bias ? a.i_bias[h] : 0.f, fb = a.f_bias ? a.f_bias[h] : 0.f;
+  const float* Sin = p.cS + ((size_t)blk * a.H + h) * D * a.V;
+  const float* nin = p.cn + ((size_t)blk * a.H + h) * D;
+  const float m0 = p.csc[((size_t)blk * a.H + h) * 4 + 2];
+  if (tid == 0 && blockIdx.z == 0 && t0 + kMcL >= e.z)
+    a.m[(size_t)e.x * a.H + h] = p.csc[((size_t)blk * a.H + h) * 4 + 3];
+  for (int i = tid; i < D * kMcCols; i += kMcThreads) {
+    const int d = i / kMcCols, c = c0 + i % kMcCols;
+    Ss[i] = c < a.V ? Sin[(size_t)d * a.V + c] : 0.f;
+  }
+  for (int d = tid; d < D; d += kMcThreads) ns[d] = nin[d];
+  mlstm_load_kv_gates(proj + (size_t)(e.y + t0) * a.ldp, a, h, len, c0, 1.f / sqrtf((float)D), ib, fb, qT, kT, vs, av, bv, true);
+  __syncthreads();
+  mlstm_block_scan(m0, av, bv, Mv);
+  __syncthreads();
+  {
+    float acc[4][4] = {};
+#pragma unroll 4
+    for (int d = 0; d < D; ++d) {
+      const float4 qa = *reinterpret_cast<const float4*>(qT + d * kMcLp + 4 * ty);
+      const float4 kb = *reinterpret_cast<const float4*>(kT + d * kMcLp + 4 * tx);
+      const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, kv[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qv[i], kv[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = 4 * ty + i, sidx = 4 * tx + j;
+        AT[sidx * kMcLp + t] = (sidx <= t) ? acc[i][j] * expf(av[sidx] - Mv[t]) : 0.f;
+      }
+  }
+  if (tid < kMcL) {
+    float d0 = 0.f;
+    for (int d = 0; d < D; ++d) d0 = fmaf(ns[d], qT[d * kMcLp + tid], d0);
+    qn[tid] = d0;
+  }
+  __syncthreads();
+  float inter[4][4] = {}, intra[4][4] = {};
+#pragma unroll 4
+  for (int d = 0; d < D; ++d) {
+    const float4 qa = *reinterpret_cast<const float4*>(qT + d * kMcLp + 4 * ty);
+    const float4 sb = *reinterpret_cast<const float4*>(Ss + d * kMcCols + 4 * tx);
+    const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, sv[4] = {sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) inter[i][j] = fmaf(qv[i], sv[j], inter[i][j]);
+  }
+  float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int sidx = 0; sidx < len; ++sidx) {
+    const float4 aa = *reinterpret_cast<const float4*>(AT + sidx * kMcLp + 4 * ty);
+    const float4 vb = *reinterpret_cast<const float4*>(vs + sidx * kMcCols + 4 * tx);
+    const float aw[4] = {aa.x, aa.y, aa.z, aa.w}, vv[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      rowsum[i] += aw[i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) intra[i][j] = fmaf(aw[i], vv[j], intra[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = 4 * ty + i;
+    if (t >= len) continue;
+    const float g = expf(m0 - Mv[t]);
+    const float den = fmaxf(fabsf(g * qn[t] + rowsum[i]), expf(-(bv[t] + Mv[t]))) + 1e-6f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + 4 * tx + j;
+      if (c < a.V) o[((size_t)(e.y + t0 + t) * a.H + h) * a.V + c] = (g * inter[i][j] + intra[i][j]) / den;
+    }
+  }
+}
+
 static size_t mlstm_chunk_smem(int D) {
   return sizeof(float) * (2 * (size_t)D * kMcLp + (size_t)D * kMcCols + kMcL * kMcLp + kMcL * kMcCols + D + 5 * kMcL);
 }
@@ -412,6 +704,48 @@ int dli_mlstm_ragged(const void* proj, float* o_scratch, void* y, const int32_t*
                         DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
     if (chunked) DLI_LAUNCH("mlstm_chunk", mlstm_chunk_kernel<float>, cgrid, dim3(kMcThreads), csmem, s, (const float*)proj, o_scratch, a);
     else DLI_LAUNCH("mlstm_scan", mlstm_scan_kernel<float>, grid, dim3(kMlThreads), smem, s, (const float*)proj, o_scratch, a);
+    DLI_LAUNCH("mlstm_out", mlstm_out_kernel<float>, dim3((rows * H + 3) / 4), dim3(128), 0, s, (const float*)o_scratch, (const float*)proj, out_w, (float*)y, rows, H, V, ldp, g_off, eps);
+  }
+  return DLI_OK;
+}
+
+size_t dli_mlstm_parallel_scratch_floats(int n_tiles, int H, int D, int V) {
+  return (size_t)n_tiles * H * ((size_t)D * V + D + 4);
+}
+
+int dli_mlstm_ragged_parallel(const void* proj, float* o_scratch, void* y, const int32_t* ent, int n_ent,
+                              const int32_t* tiles, int n_tiles, float* scratch, int rows, int H, int D, int V, int ldp,
+                              int q_off, int k_off, int v_off, int i_off, int f_off, int g_off, const float* i_bias,
+                              const float* f_bias, float cap, const float* out_w, float eps, float* S, float* n, float* m,
+                              int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(proj && o_scratch && y && ent && tiles && scratch && out_w && S && n && m, "dli_mlstm_ragged_parallel: null pointer");
+  DLI_CHECK_ARG(H > 0 && D > 0 && V > 0, "dli_mlstm_ragged_parallel: empty shape");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  const size_t csmem = mlstm_chunk_smem(D);
+  if (csmem > 220 * 1024) return dli::fail(DLI_ERR_UNSUPPORTED, "dli_mlstm_ragged_parallel: key size %d is too large for the block form", D);
+  if (rows <= 0 || n_ent <= 0 || n_tiles <= 0) return DLI_OK;
+  MlstmArgs a{ent, H, D, V, ldp, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, cap, S, n, m};
+  MlstmPar p{tiles, scratch, scratch + (size_t)n_tiles * H * D * V, scratch + (size_t)n_tiles * H * ((size_t)D * V + D)};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 bgrid(n_tiles, H, (V + kMcCols - 1) / kMcCols);
+  const size_t lsmem = sizeof(float) * ((size_t)D * kMcLp + kMcL * kMcCols + 4 * kMcL);
+  const size_t total = (size_t)D * V + D;
+  const dim3 cgrid(n_ent, H, (unsigned)((total + 255) / 256));
+  if (dt == 0) {
+    static PerDeviceOnce once;
+    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_par_local_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+                        DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_par_readout_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
+    DLI_LAUNCH("mlstm_par_local", mlstm_par_local_kernel<bf16>, bgrid, dim3(kMcThreads), lsmem, s, (const bf16*)proj, a, p);
+    DLI_LAUNCH("mlstm_par_carry", mlstm_par_carry_kernel, cgrid, dim3(256), 0, s, a, p, n_tiles);
+    DLI_LAUNCH("mlstm_par_readout", mlstm_par_readout_kernel<bf16>, bgrid, dim3(kMcThreads), csmem, s, (const bf16*)proj, o_scratch, a, p);
+    DLI_LAUNCH("mlstm_out", mlstm_out_kernel<bf16>, dim3((rows * H + 3) / 4), dim3(128), 0, s, (const float*)o_scratch, (const bf16*)proj, out_w, (bf16*)y, rows, H, V, ldp, g_off, eps);
+  } else {
+    static PerDeviceOnce once;
+    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_par_local_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+                        DLI_CUDA_CALL(cudaFuncSetAttribute(mlstm_par_readout_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
+    DLI_LAUNCH("mlstm_par_local", mlstm_par_local_kernel<float>, bgrid, dim3(kMcThreads), lsmem, s, (const float*)proj, a, p);
+    DLI_LAUNCH("mlstm_par_carry", mlstm_par_carry_kernel, cgrid, dim3(256), 0, s, a, p, n_tiles);
+    DLI_LAUNCH("mlstm_par_readout", mlstm_par_readout_kernel<float>, bgrid, dim3(kMcThreads), csmem, s, (const float*)proj, o_scratch, a, p);
     DLI_LAUNCH("mlstm_out", mlstm_out_kernel<float>, dim3((rows * H + 3) / 4), dim3(128), 0, s, (const float*)o_scratch, (const float*)proj, out_w, (float*)y, rows, H, V, ldp, g_off, eps);
   }
   return DLI_OK;

@@ -568,3 +568,22 @@ def mlstm_ragged(proj, o_scratch, out, ent, H, D, V, q_off, k_off, v_off, i_off,
           proj.shape[1], q_off, k_off, v_off, i_off, f_off, g_off, _p(i_bias), _p(f_bias), float(cap), _p(out_w),
           float(eps), _p(S), _p(n), _p(m), int(bool(blocked)), _dt(proj), _stream())
     return out
+
+
+def mlstm_parallel_scratch_floats(n_tiles, H, D, V) -> int:
+    return int(_lib.load().dli_mlstm_parallel_scratch_floats(int(n_tiles), int(H), int(D), int(V)))
+
+
+def mlstm_ragged_parallel(proj, o_scratch, out, ent, tiles, scratch, H, D, V, q_off, k_off, v_off, i_off, f_off, g_off,
+                          i_bias, f_bias, cap, out_w, eps, S, n, m):
+    """mlstm_ragged for steps with long portions: the 64-position blocks of every entry run in parallel (local state
+    contributions, an ordered elementwise carry, read-outs).  tiles int32 [n_tiles, 2] = (entry, first row of the block
+    within the entry), blocks of an entry consecutive; scratch: mlstm_parallel_scratch_floats(...) float32."""
+    _req(proj, proj.dtype), _req(out, proj.dtype), _f32(o_scratch, i_bias, f_bias, out_w, S, n, m, scratch), _i32(ent, tiles)
+    n_tiles = tiles.numel() // 2
+    if scratch.numel() < mlstm_parallel_scratch_floats(n_tiles, H, D, V):
+        raise ValueError("mlstm_ragged_parallel: scratch too small")
+    _call("dli_mlstm_ragged_parallel", 4, _p(proj), _p(o_scratch), _p(out), _p(ent), ent.numel() // 4, _p(tiles), n_tiles,
+          _p(scratch), proj.shape[0], H, D, V, proj.shape[1], q_off, k_off, v_off, i_off, f_off, g_off, _p(i_bias),
+          _p(f_bias), float(cap), _p(out_w), float(eps), _p(S), _p(n), _p(m), _dt(proj), _stream())
+    return out

@@ -144,6 +144,7 @@ class RaggedEngine:
         self.pad_token_id: Optional[int] = None
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
         self.tc_min_rows = int(os.environ.get("DLI_RAGGED_TC_MIN_ROWS", "16"))  # portions from this size: tensor-core attention
+        self.mlstm_parallel_max_floats = 1 << 28   # scratch bound (1 GiB) of the block-parallel mLSTM; beyond it: blocks in order
         self.layer_trace: Optional[list] = None    # set to [] to collect the residual stream after every layer
         ops.set_pdl(os.environ.get("DLI_PDL", "1") == "1")
 
@@ -309,7 +310,7 @@ class RaggedEngine:
             self.kv.commit()
         # steps that hold a portion of a prompt run attention in 64-row query tiles on the tensor cores
         tiles: List[int] = []
-        if self.dtype == BF and any(len(t) >= self.tc_min_rows for _, t in batch):
+        if any(len(t) >= self.tc_min_rows for _, t in batch):
             for i, (_, toks) in enumerate(batch):
                 for q0 in range(0, len(toks), 64):
                     tiles += [i, q0]
@@ -420,9 +421,20 @@ class RaggedEngine:
                                     sin_v=sv)
             else:
                 oscr = self._oscr[:rows * n_mix]
-                ops.mlstm_ragged(proj, oscr, mix, d_ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"], off["i"],
-                                 off["f"], off["g"], P["i_b"], P["f_b"], m.gate_cap, P["out_norm"], s.eps,
-                                 self.slots[("S", li)], self.slots[("n", li)], self.slots[("m", li)], blocked=long_step)
+                n_tiles = d_tiles.numel() // 2
+                need = ops.mlstm_parallel_scratch_floats(n_tiles, m.heads, m.dim, m.vdim) if tiles and n_tiles > n_ent else 0
+                if need and need <= self.mlstm_parallel_max_floats and m.dim <= 224:
+                    # some entry spans several 64-position blocks: all blocks in parallel
+                    if getattr(self, "_mlstm_scr", None) is None or self._mlstm_scr.numel() < need:
+                        self._mlstm_scr = torch.empty(need, dtype=torch.float32, device=dev)
+                    ops.mlstm_ragged_parallel(proj, oscr, mix, d_ent, d_tiles, self._mlstm_scr, m.heads, m.dim, m.vdim,
+                                              off["q"], off["k"], off["v"], off["i"], off["f"], off["g"], P["i_b"],
+                                              P["f_b"], m.gate_cap, P["out_norm"], s.eps, self.slots[("S", li)],
+                                              self.slots[("n", li)], self.slots[("m", li)])
+                else:
+                    ops.mlstm_ragged(proj, oscr, mix, d_ent, m.heads, m.dim, m.vdim, off["q"], off["k"], off["v"], off["i"],
+                                     off["f"], off["g"], P["i_b"], P["f_b"], m.gate_cap, P["out_norm"], s.eps,
+                                     self.slots[("S", li)], self.slots[("n", li)], self.slots[("m", li)], blocked=long_step)
             self._lin(mix, P["wo"], y)
             g_post = P["norm1b"]
             if L.ff:

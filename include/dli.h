@@ -455,6 +455,16 @@ int dli_mlstm_ragged(const void* proj, float* o_scratch, void* y, const int32_t*
                      const float* i_bias, const float* f_bias, float cap, const float* out_w, float eps, float* S,
                      float* n, float* m, int blocked, int dt, dli_stream_t stream);
 
+/* The same layer for steps with long portions: every 64-position block of every entry gets its own CTAs (local state
+ * contributions in parallel, an elementwise carry over the blocks in order, read-outs in parallel).  tiles as for
+ * dli_attn_ragged_tc; scratch: dli_mlstm_parallel_scratch_floats(n_tiles, H, D, V) floats. */
+size_t dli_mlstm_parallel_scratch_floats(int n_tiles, int H, int D, int V);
+int dli_mlstm_ragged_parallel(const void* proj, float* o_scratch, void* y, const int32_t* ent, int n_ent,
+                              const int32_t* tiles, int n_tiles, float* scratch, int rows, int H, int D, int V, int ldp,
+                              int q_off, int k_off, int v_off, int i_off, int f_off, int g_off, const float* i_bias,
+                              const float* f_bias, float cap, const float* out_w, float eps, float* S, float* n, float* m,
+                              int dt, dli_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

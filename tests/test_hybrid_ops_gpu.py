@@ -272,17 +272,18 @@ def mlstm_oracle(q, k, v, g, ig, fg, m, ib, fb, nw, eps):
 
 
 @pytest.mark.parametrize("dims", [(2, 48, 64), (3, 10, 40), (1, 130, 33)])
-@pytest.mark.parametrize("cuts", [[90], [1] * 90, [2, 2, 31, 1, 1, 40, 13], [70, 20]])
-@pytest.mark.parametrize("blocked", [False, True])
+@pytest.mark.parametrize("cuts", [[90], [1] * 90, [2, 2, 31, 1, 1, 40, 13], [70, 20], [300]])
+@pytest.mark.parametrize("blocked", [False, True, "parallel"])
 def test_mlstm_portions_and_dirty_slots(dims, cuts, blocked):
-    """Token by token (blocked=False) and 64 positions at a time (blocked=True: portions longer and shorter than a
-    block, a block that ends inside a portion) against the oracle's loop."""
+    """Token by token (blocked=False), 64 positions at a time in order (True) and with the blocks of a portion in
+    parallel ("parallel"): portions longer and shorter than a block, a block that ends inside a portion, against the
+    oracle's loop."""
     from dli_b200 import ops
 
     H, D, V = dims
     torch.manual_seed(6)
     m = {"heads": H, "dim": D, "vdim": V, "gate_cap": 6.0}
-    T = 90
+    T = 90 if cuts != [300] else 300
     q, k, v, g = torch.randn(T, H * D), torch.randn(T, H * D), torch.randn(T, H * V), torch.randn(T, H * V)
     ig, fg = 4 * torch.randn(T, H), 4 * torch.randn(T, H) + 2   # beyond the cap on both sides
     ib, fb, nw = torch.randn(H), torch.randn(H), torch.rand(H * V) + 0.5
@@ -300,9 +301,15 @@ def test_mlstm_portions_and_dirty_slots(dims, cuts, blocked):
         _, ent = meta([(2, c, at)])
         pr = proj[at:at + c].contiguous()
         o = torch.empty(c, H * V, device=DEV)
-        ops.mlstm_ragged(pr, torch.empty(c * H * V, device=DEV), o, ent, H, D, V, 0, H * D, 2 * H * D,
-                         2 * H * D + 2 * H * V, 2 * H * D + 2 * H * V + H, 2 * H * D + H * V, ib.to(DEV), fb.to(DEV),
-                         6.0, nw.to(DEV), 1e-5, S, n, mm, blocked=blocked)
+        offs = (0, H * D, 2 * H * D, 2 * H * D + 2 * H * V, 2 * H * D + 2 * H * V + H, 2 * H * D + H * V)
+        if blocked == "parallel":
+            tiles = torch.tensor([[0, q0] for q0 in range(0, c, 64)], dtype=torch.int32, device=DEV)
+            scr = torch.full((ops.mlstm_parallel_scratch_floats(tiles.shape[0], H, D, V),), float("nan"), device=DEV)
+            ops.mlstm_ragged_parallel(pr, torch.empty(c * H * V, device=DEV), o, ent, tiles, scr, H, D, V, *offs,
+                                      ib.to(DEV), fb.to(DEV), 6.0, nw.to(DEV), 1e-5, S, n, mm)
+        else:
+            ops.mlstm_ragged(pr, torch.empty(c * H * V, device=DEV), o, ent, H, D, V, *offs, ib.to(DEV), fb.to(DEV),
+                             6.0, nw.to(DEV), 1e-5, S, n, mm, blocked=blocked)
         out[at:at + c] = o
         at += c
     assert at == T
