@@ -72,6 +72,7 @@ SIGNATURES = {
     "dli_scalar_rmsnorm_f32": (_i, [_vp, _vp, _i, _i, _f, _f, _vp]),
     "dli_postnorm_add_norm": (_i, [_vp, _vp, _vp, _i, _i, _f, _f, _f, _i, _vp]),
     "dli_causal_conv_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "dli_postnorm_add_norm_conv_single": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _f, _i, _vp]),
     "dli_gather_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_linear_any": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_silu_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),

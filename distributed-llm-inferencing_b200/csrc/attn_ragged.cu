@@ -57,7 +57,8 @@ attn_prep_append_kernel(const E* __restrict__ proj, float* __restrict__ qbuf, E*
   const int pos = e.w + (row - e.y);
   const int page = a.page_table[(size_t)e.x * a.max_pages + pos / a.page_size], off = pos % a.page_size;
   const E* pr = proj + (size_t)row * a.ldp;
-  for (int item = warp; item < a.H + 2 * a.G; item += 4) {
+  // grid.y spreads the heads of a row over CTAs (a decode row would otherwise walk all heads with four warps)
+  for (int item = blockIdx.y * 4 + warp; item < a.H + 2 * a.G; item += 4 * gridDim.y) {
     if (item < a.H + a.G) {
       const bool is_q = item < a.H;
       const int hh = is_q ? item : item - a.H;
@@ -472,8 +473,10 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
   AttnPrep a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, rd, ldp, q_off, k_off, v_off, q_norm, k_norm,
              eps, (rd > 0 ? cos_qk : nullptr), sin_qk, cos_v, sin_v, table_len};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<bf16>, dim3(rows), dim3(128), 0, s, (const bf16*)proj, qbuf, (bf16*)k_cache, (bf16*)v_cache, a);
-  else DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<float>, dim3(rows), dim3(128), 0, s, (const float*)proj, qbuf, (float*)k_cache, (float*)v_cache, a);
+  const int items = H + 2 * G;
+  const dim3 pgrid(rows, rows <= 64 ? (items + 3) / 4 : 1);
+  if (dt == 0) DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<bf16>, pgrid, dim3(128), 0, s, (const bf16*)proj, qbuf, (bf16*)k_cache, (bf16*)v_cache, a);
+  else DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<float>, pgrid, dim3(128), 0, s, (const float*)proj, qbuf, (float*)k_cache, (float*)v_cache, a);
   return DLI_OK;
 }
 

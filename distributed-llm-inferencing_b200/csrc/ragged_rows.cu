@@ -33,7 +33,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 // x[row] = table[ids[row]] as fp32 (the residual stream starts in fp32).
 template <typename E>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ table, float* __restrict__ x, int d, int vocab) {
   pdl_wait();
   pdl_trigger();
@@ -44,9 +44,9 @@ embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ tabl
 }
 
 // hn = x / sqrt(mean(x^2) + eps) * g  with ONE weight g for the whole row.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 scalar_rmsnorm_kernel(const float* __restrict__ x, float* __restrict__ hn, int d, float eps, float g) {
-  __shared__ float red[8];
+  __shared__ float red[32];
   pdl_wait();
   pdl_trigger();
   const float* xr = x + (size_t)blockIdx.x * d;
@@ -60,10 +60,10 @@ scalar_rmsnorm_kernel(const float* __restrict__ x, float* __restrict__ hn, int d
 // x += y / sqrt(mean(y^2) + eps) * g_post; then (hn != NULL) hn = x / sqrt(mean(x^2) + eps) * g_next:
 // the post-norm of one sublayer, the fp32 residual add and the pre-norm of the next sublayer in one pass.
 template <typename E>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 postnorm_add_norm_kernel(const E* __restrict__ y, float* __restrict__ x, float* __restrict__ hn, int d, float eps,
                          float g_post, float g_next) {
-  __shared__ float red[8];
+  __shared__ float red[32];
   pdl_wait();
   pdl_trigger();
   const size_t o = (size_t)blockIdx.x * d;
@@ -135,6 +135,74 @@ causal_conv_single_kernel(const float* __restrict__ h, float* __restrict__ tail,
     }
     if (keep > 0) t[(size_t)(keep - 1) * d] = cur;
     out[(size_t)row * d + c] = from_f<E>(cur + acc);
+  }
+}
+
+// Decode rows (one row per entry): the post-norm of a sublayer, the fp32 residual add, the pre-norm of the next
+// sublayer AND that sublayer's input convolution with its tail shift in one kernel (y == NULL: no post-norm part,
+// the row of x is normed and convolved as it is — the first sublayer after the embedding).
+template <typename E>
+__global__ void __launch_bounds__(1024)
+postnorm_add_norm_conv_single_kernel(const E* __restrict__ y, float* __restrict__ x, float* __restrict__ tail,
+                                     const float* __restrict__ w, const int32_t* __restrict__ ent, E* __restrict__ out,
+                                     int d, int taps, float eps, float g_post, float g_next) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  const size_t o = (size_t)row * d;
+  float s2 = 0.f;
+  if (y != nullptr) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      const float v = to_f(y[o + c]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = g_post / sqrtf(ss / d + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      const float v = x[o + c] + to_f(y[o + c]) * r;
+      x[o + c] = v;
+      s2 += v * v;
+    }
+  } else {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) s2 += x[o + c] * x[o + c];
+  }
+  s2 = block_sum(s2, red);
+  const float r2 = g_next / sqrtf(s2 / d + eps);
+  const int4 e = reinterpret_cast<const int4*>(ent)[row];
+  const int keep = taps - 1;
+  constexpr int kMaxKeep = 7;  // up to 8 taps: all tail values and weights of a channel are loaded before any is used
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float* t = tail + (size_t)e.x * keep * d + c;
+    const float cur = x[o + c] * r2;
+    if (keep <= kMaxKeep) {
+      float tv[kMaxKeep], wv[kMaxKeep + 1];
+#pragma unroll
+      for (int i = 0; i < kMaxKeep; ++i) {
+        tv[i] = (i < keep && e.w - keep + i >= 0) ? t[(size_t)i * d] : 0.f;
+        wv[i] = i < keep ? w[(size_t)c * taps + i] : 0.f;
+      }
+      float acc = w[(size_t)c * taps + keep] * cur;
+#pragma unroll
+      for (int i = 0; i < kMaxKeep; ++i) {
+        if (i < keep) {
+          acc += wv[i] * tv[i];
+          if (i > 0) t[(size_t)(i - 1) * d] = tv[i];
+        }
+      }
+      if (keep > 0) t[(size_t)(keep - 1) * d] = cur;
+      out[o + c] = from_f<E>(cur + acc);
+      continue;
+    }
+    float acc = w[(size_t)c * taps + keep] * cur;
+    for (int i = 0; i < keep; ++i) {
+      const float v = (e.w - keep + i >= 0) ? t[(size_t)i * d] : 0.f;
+      acc += w[(size_t)c * taps + i] * v;
+      if (i > 0) t[(size_t)(i - 1) * d] = v;
+    }
+    t[(size_t)(keep - 1) * d] = cur;
+    out[o + c] = from_f<E>(cur + acc);
   }
 }
 
@@ -230,6 +298,9 @@ using namespace dli;
 
 #define DT_CHECK(dt) DLI_CHECK_ARG((dt) == 0 || (dt) == 1, "element type %d: 0 = bf16, 1 = float", dt)
 
+// few rows of a wide model: one CTA per row needs many threads to cover the row's latency; many rows: 256 are enough
+static inline int row_threads(int rows, int d) { return (rows <= 64 && d >= 2048) ? 1024 : 256; }
+
 extern "C" {
 
 int dli_embedding_f32(const int32_t* ids, const void* table, float* x, int rows, int d, int vocab, int dt,
@@ -238,15 +309,15 @@ int dli_embedding_f32(const int32_t* ids, const void* table, float* x, int rows,
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(128), 0, s, ids, (const bf16*)table, x, d, vocab);
-  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(128), 0, s, ids, (const float*)table, x, d, vocab);
+  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, d, vocab);
+  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, d, vocab);
   return DLI_OK;
 }
 
 int dli_scalar_rmsnorm_f32(const float* x, float* hn, int rows, int d, float eps, float g, dli_stream_t stream) {
   DLI_CHECK_ARG(x && hn && d > 0, "dli_scalar_rmsnorm_f32: null pointer or empty shape");
   if (rows <= 0) return DLI_OK;
-  DLI_LAUNCH("scalar_rmsnorm", scalar_rmsnorm_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), x, hn, d, eps, g);
+  DLI_LAUNCH("scalar_rmsnorm", scalar_rmsnorm_kernel, dim3(rows), dim3(row_threads(rows, d)), 0, static_cast<cudaStream_t>(stream), x, hn, d, eps, g);
   return DLI_OK;
 }
 
@@ -256,8 +327,8 @@ int dli_postnorm_add_norm(const void* y, float* x, float* hn, int rows, int d, f
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("postnorm_add_norm", postnorm_add_norm_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)y, x, hn, d, eps, g_post, g_next);
-  else DLI_LAUNCH("postnorm_add_norm", postnorm_add_norm_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)y, x, hn, d, eps, g_post, g_next);
+  if (dt == 0) DLI_LAUNCH("postnorm_add_norm", postnorm_add_norm_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, (const bf16*)y, x, hn, d, eps, g_post, g_next);
+  else DLI_LAUNCH("postnorm_add_norm", postnorm_add_norm_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, (const float*)y, x, hn, d, eps, g_post, g_next);
   return DLI_OK;
 }
 
@@ -277,6 +348,19 @@ int dli_causal_conv_ragged(const float* h, float* tail, const float* w, const in
   if (dt == 0) DLI_LAUNCH("causal_conv", causal_conv_kernel<bf16>, dim3(rows), dim3(256), 0, s, h, (const float*)tail, w, row_ent, ent, (bf16*)out, d, taps);
   else DLI_LAUNCH("causal_conv", causal_conv_kernel<float>, dim3(rows), dim3(256), 0, s, h, (const float*)tail, w, row_ent, ent, (float*)out, d, taps);
   if (taps > 1) DLI_LAUNCH("conv_tail_update", conv_tail_update_kernel, dim3(n_ent), dim3(256), 0, s, h, tail, ent, d, taps);
+  return DLI_OK;
+}
+
+int dli_postnorm_add_norm_conv_single(const void* y, float* x, float* tail, const float* w, const int32_t* ent, void* out,
+                                      int rows, int d, int taps, float eps, float g_post, float g_next, int dt,
+                                      dli_stream_t stream) {
+  DLI_CHECK_ARG(x && w && ent && out && d > 0 && taps >= 1 && (tail || taps == 1), "dli_postnorm_add_norm_conv_single: null pointer or empty shape");
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_postnorm_add_norm_conv_single: ent must be 16-byte aligned");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("postnorm_add_norm_conv_single", postnorm_add_norm_conv_single_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, (const bf16*)y, x, tail, w, ent, (bf16*)out, d, taps, eps, g_post, g_next);
+  else DLI_LAUNCH("postnorm_add_norm_conv_single", postnorm_add_norm_conv_single_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, (const float*)y, x, tail, w, ent, (float*)out, d, taps, eps, g_post, g_next);
   return DLI_OK;
 }
 

@@ -587,3 +587,15 @@ def mlstm_ragged_parallel(proj, o_scratch, out, ent, tiles, scratch, H, D, V, q_
           _p(scratch), proj.shape[0], H, D, V, proj.shape[1], q_off, k_off, v_off, i_off, f_off, g_off, _p(i_bias),
           _p(f_bias), float(cap), _p(out_w), float(eps), _p(S), _p(n), _p(m), _dt(proj), _stream())
     return out
+
+
+def postnorm_add_norm_conv_single(y, x, tail, w, ent, out, g_post: float, g_next: float, eps: float):
+    """Decode rows (one per entry): x += y / rms(y) * g_post (skipped when y is None), h = x / rms(x) * g_next,
+    out = h + conv(h) with the slot's tail shifted — postnorm_add_norm and the next sublayer's causal_conv_ragged
+    as one kernel."""
+    _f32(x, tail, w), _i32(ent), _req(out, out.dtype)
+    if y is not None:
+        _req(y, out.dtype)
+    _call("dli_postnorm_add_norm_conv_single", 1, _p(y), _p(x), _p(tail), _p(w), _p(ent), _p(out), x.shape[0], x.shape[1],
+          w.shape[1], float(eps), float(g_post), float(g_next), _dt(out), _stream())
+    return out

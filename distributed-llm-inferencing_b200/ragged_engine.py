@@ -219,6 +219,7 @@ class RaggedEngine:
 
     def unload(self) -> None:
         self._graphs.clear()
+        self._sk = None
         self.w.clear()
         self.layers.clear()
         self.kv.release_all()
@@ -271,8 +272,20 @@ class RaggedEngine:
         """out = x @ w.T: the framework's bf16 projection (tcgen05 GEMM / weight-streaming GEMV) where its alignment
         rules hold, else the CUDA-core GEMM (float32 engines, odd shapes)."""
         if self.dtype == BF and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+            if 2 < x.shape[0] <= 128 and x.shape[1] % 64 == 0 and w.shape[0] % 16 == 0:
+                # few rows (batched decode, short portions): the split-K weight stream on every SM, as the uniform
+                # stacks' batched decode does
+                return ops.linear_splitk(x, w, self._splitk(), out=out)
             return ops.linear(x, w, out=out)
         return ops.linear_any(x, w, out)
+
+    def _splitk(self) -> torch.Tensor:
+        """Zero-filled scratch of the split-K projections (self-resetting; calls are ordered on one stream)."""
+        if getattr(self, "_sk", None) is None:
+            n_max = max([self.w["head"].shape[0]] + [max(d["w_proj"].shape[0], d["w_gu"].shape[0] if "w_gu" in d else 0,
+                                                         self.spec.width) for d in self.layers.values()])
+            self._sk = torch.zeros(ops.gemm_splitk_scratch_bytes(128, n_max), dtype=torch.uint8, device=self.device)
+        return self._sk
 
     # ------------------------------------------------------------------ one step
     def step(self, batch: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]] = None):
@@ -388,15 +401,29 @@ class RaggedEngine:
         W = s.width
         x, hn, hc = self._x[:rows], self._hn[:rows], self._hc[:rows]
         y = self._y[:rows]
-        ops.embedding_f32(d_tok, self.w["embed"], x)
-        ops.scalar_rmsnorm(x, self.layers[s.source(0)]["norm1"], s.eps, hn)
-        pt = self.kv.page_table
-        for li, L in enumerate(s.layers):
-            P, m = self.layers[s.source(li)], L.mixer
+        single = rows == n_ent and s.taps > 1 and self.layer_trace is None  # decode rows: norm + convolution fused
+
+        def enter_sublayer(y_prev, g_post, g_next, tail, taps_w):
+            """Close the previous sublayer (x += postnorm(y_prev)) and open the next one: hc = its normed and convolved
+            input.  One kernel for decode rows, norm kernel + convolution (+ tail shift) otherwise."""
+            if single:
+                ops.postnorm_add_norm_conv_single(y_prev, x, tail, taps_w, d_ent, hc, g_post, g_next, s.eps)
+                return
+            if y_prev is None:
+                ops.scalar_rmsnorm(x, g_next, s.eps, hn)
+            else:
+                ops.postnorm_add_norm(y_prev, x, g_post, s.eps, hn, g_next)
             if s.taps > 1:
-                ops.causal_conv_ragged(hn, self.slots[("tail1", li)], P["canon1"], d_rent, d_ent, hc)
+                ops.causal_conv_ragged(hn, tail, taps_w, d_rent, d_ent, hc)
             else:
                 ops.gather_cast(hn, self._iota(rows), hc)
+
+        ops.embedding_f32(d_tok, self.w["embed"], x)
+        pt = self.kv.page_table
+        y_prev, g_prev = None, 1.0
+        for li, L in enumerate(s.layers):
+            P, m = self.layers[s.source(li)], L.mixer
+            enter_sublayer(y_prev, g_prev, P["norm1"], self.slots.tensors.get(("tail1", li)), P.get("canon1"))
             n_proj = P["w_proj"].shape[0]
             proj = self._proj[:rows * n_proj].view(rows, n_proj)
             self._lin(hc, P["w_proj"], proj)
@@ -438,13 +465,11 @@ class RaggedEngine:
             self._lin(mix, P["wo"], y)
             g_post = P["norm1b"]
             if L.ff:
-                ops.postnorm_add_norm(y, x, g_post, s.eps, hn, P["norm2"])
-                if s.taps > 1:
-                    ops.causal_conv_ragged(hn, self.slots[("tail2", li)], P["canon2"], d_rent, d_ent, hc)
-                else:
-                    ops.gather_cast(hn, self._iota(rows), hc)
+                enter_sublayer(y, g_post, P["norm2"], self.slots.tensors.get(("tail2", li)), P.get("canon2"))
                 act = self._act[:rows * L.ff].view(rows, L.ff)
-                if P["packed"]:
+                if P["packed"] and 2 < rows <= 128 and W % 64 == 0:
+                    ops.linear_splitk_gated_silu(hc, P["w_gu"], self._splitk(), out=act)
+                elif P["packed"]:
                     ops.linear_gated_silu(hc, P["w_gu"], out=act)
                 else:
                     gu = self._gu[:rows * 2 * L.ff].view(rows, 2 * L.ff)
@@ -452,10 +477,16 @@ class RaggedEngine:
                     ops.silu_mul(gu, act)
                 self._lin(act, P["w_down"], y)
                 g_post = P["norm2b"]
-            g_next = self.layers[s.source(li + 1)]["norm1"] if li + 1 < s.n_layers else self.w["final_norm"]
-            ops.postnorm_add_norm(y, x, g_post, s.eps, hn, g_next)
+            y_prev, g_prev = y, g_post
             if self.layer_trace is not None:
+                # the residual stream after the layer (debugging): close the sublayer now and open the next without it
+                ops.postnorm_add_norm(y, x, g_post, s.eps)
                 self.layer_trace.append(x.clone())
+                y_prev = None
+        if y_prev is None:
+            ops.scalar_rmsnorm(x, self.w["final_norm"], s.eps, hn)
+        else:
+            ops.postnorm_add_norm(y_prev, x, g_prev, s.eps, hn, self.w["final_norm"])
         if nw == 0:
             return None
         hw = self._hw[:nw] if nw <= self._hw.shape[0] else torch.empty(nw, W, dtype=E, device=dev)

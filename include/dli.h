@@ -412,6 +412,11 @@ int dli_postnorm_add_norm(const void* y, float* x, float* hn, int rows, int d, f
  * tail [slots, taps-1, d] fp32 holds each sequence's last inputs and is advanced by the call. */
 int dli_causal_conv_ragged(const float* h, float* tail, const float* w, const int32_t* row_ent, const int32_t* ent,
                            void* out, int rows, int n_ent, int d, int taps, int dt, dli_stream_t stream);
+/* Steps of one row per entry (decode): dli_postnorm_add_norm followed by dli_causal_conv_ragged of the NEXT sublayer as
+ * one kernel; y == NULL skips the post-norm and residual add (the first sublayer after the embedding). */
+int dli_postnorm_add_norm_conv_single(const void* y, float* x, float* tail, const float* w, const int32_t* ent, void* out,
+                                      int rows, int d, int taps, float eps, float g_post, float g_next, int dt,
+                                      dli_stream_t stream);
 int dli_gather_cast(const float* src, const int32_t* rows, void* out, int n, int d, int dt, dli_stream_t stream);
 /* y[M,N] = x[M,K] . w[N,K]^T on the CUDA cores with fp32 accumulation: any shape, both element types. */
 int dli_linear_any(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldy, int dt,
