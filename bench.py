@@ -423,8 +423,19 @@ def run_hybrid_compare(args, peaks):
     T, K, W = args.ctx, args.steps, args.warmup
     out = {"metric": "hybrid_vs_uniform", "unit": "tokens/s", "ctx": T, "steps": K, "warmup": W, "dtype": "bf16",
            "data": "synthetic", "peaks": peaks, "sizes": {}}
+    names = args.hybrid_sizes.split(",")
+    if len(names) > 1:
+        # one process per size: a size measured after another one in the same process inherits its allocator and
+        # graph-pool state (the batch-8 decode of the second size came out up to 10x slower that way)
+        import subprocess
+        for name in names:
+            cmd = [sys.executable, os.path.abspath(__file__), "--compare-hybrid", "--hybrid-sizes", name, "--steps", str(K),
+                   "--warmup", str(W), "--ctx", str(T), "--batch", str(args.batch), "--page-size", str(args.page_size)]
+            p = subprocess.run(cmd, capture_output=True, text=True, check=True)
+            out["sizes"].update(json.loads(p.stdout.strip().splitlines()[-1])["sizes"])
+        return out
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > L2: written between timed prefills
-    for name in args.hybrid_sizes.split(","):
+    for name in names:
         width, heads, kv, hd, ff, layers, vocab = HYBRID_SIZES[name]
         res = {}
         # ---- the new family

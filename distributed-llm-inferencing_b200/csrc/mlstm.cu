@@ -524,19 +524,31 @@ mlstm_par_carry_kernel(MlstmArgs a, MlstmPar p, int n_tiles) {
   if (idx < DV) state = a.S + ((size_t)e.x * a.H + h) * DV + idx;
   else if (idx < total) state = a.n + ((size_t)e.x * a.H + h) * a.D + (idx - DV);
   float sv = (state && !fresh) ? *state : 0.f;
-  for (int b = 0; b < nblk; ++b) {
-    const int blk = first + b;
-    float* sc = p.csc + ((size_t)blk * a.H + h) * 4;
-    const float bL = sc[0], A = sc[1];
-    const float M = fmaxf(m0, A), g = expf(m0 - M), w = expf(A - M);
-    if (state) {
-      float* slot = idx < DV ? p.cS + ((size_t)blk * a.H + h) * DV + idx : p.cn + ((size_t)blk * a.H + h) * a.D + (idx - DV);
-      const float u = *slot;
-      *slot = sv;
-      sv = g * sv + w * u;
+  // eight blocks at a time: all their loads are issued before the first store, so the chain is the arithmetic only
+  for (int b0 = 0; b0 < nblk; b0 += 8) {
+    float bL[8], A[8], u[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int blk = first + min(b0 + j, nblk - 1);
+      const float* sc = p.csc + ((size_t)blk * a.H + h) * 4;
+      bL[j] = sc[0];
+      A[j] = sc[1];
+      u[j] = 0.f;
+      if (state) u[j] = idx < DV ? p.cS[((size_t)blk * a.H + h) * DV + idx] : p.cn[((size_t)blk * a.H + h) * a.D + (idx - DV)];
     }
-    if (idx == 0) sc[2] = m0;
-    m0 = bL + M;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (b0 + j >= nblk) break;
+      const int blk = first + b0 + j;
+      const float M = fmaxf(m0, A[j]), g = expf(m0 - M), w = expf(A[j] - M);
+      if (state) {
+        float* slot = idx < DV ? p.cS + ((size_t)blk * a.H + h) * DV + idx : p.cn + ((size_t)blk * a.H + h) * a.D + (idx - DV);
+        *slot = sv;
+        sv = g * sv + w * u[j];
+      }
+      if (idx == 0) p.csc[((size_t)blk * a.H + h) * 4 + 2] = m0;
+      m0 = bL[j] + M;
+    }
   }
   if (state) *state = sv;
   // the slot's m is read by every CTA of this pass: its new value waits in the last block's scalars until pass 3
