@@ -19,3 +19,14 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _collect_dead_engines():
+    """Engines own captured CUDA graphs.  One that a finished test left in a reference cycle (a traceback frame, a
+    future) would otherwise be destroyed by whichever allocation triggers the collector — possibly in the middle of
+    another test's graph capture, where destroying a graph is not permitted.  Collect at the test boundary instead."""
+    yield
+    import gc
+
+    gc.collect()
