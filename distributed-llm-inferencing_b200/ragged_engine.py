@@ -66,7 +66,7 @@ class HybridSpec:
     vocab: int
     width: int
     eps: float
-    taps: int                      # taps of the input convolutions (1 = none)
+    taps: int                      # taps of the input convolutions (1: the current input only, no state)
     layers: List[LayerSpec] = field(default_factory=list)
 
     @property
@@ -182,8 +182,7 @@ class RaggedEngine:
         for i, src in t["layers"].items():
             L, m = s.layers[i], s.layers[i].mixer
             d = {"norm1": float(src["norm1"]), "norm1b": float(src["norm1b"])}
-            if s.taps > 1:
-                d["canon1"] = src["canon1"].to(torch.float32).contiguous().to(dev)
+            d["canon1"] = src["canon1"].to(torch.float32).contiguous().to(dev)
             qn, kn, vn = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
             if m.kind == "attention":
                 d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"]) if m.head_gate else mat(src["q"], src["k"], src["v"])
@@ -200,8 +199,7 @@ class RaggedEngine:
             d["wo"] = mat(src["o"], pad_rows=False)
             if L.ff:
                 d["norm2"], d["norm2b"] = float(src["norm2"]), float(src["norm2b"])
-                if s.taps > 1:
-                    d["canon2"] = src["canon2"].to(torch.float32).contiguous().to(dev)
+                d["canon2"] = src["canon2"].to(torch.float32).contiguous().to(dev)
                 # the tensor-core path interleaves gate and up rows so that silu(gate) * up is the GEMM's epilogue
                 d["packed"] = E == BF and L.ff % 128 == 0 and s.width % 8 == 0
                 if d["packed"]:
@@ -413,10 +411,7 @@ class RaggedEngine:
                 ops.scalar_rmsnorm(x, g_next, s.eps, hn)
             else:
                 ops.postnorm_add_norm(y_prev, x, g_post, s.eps, hn, g_next)
-            if s.taps > 1:
-                ops.causal_conv_ragged(hn, tail, taps_w, d_rent, d_ent, hc)
-            else:
-                ops.gather_cast(hn, self._iota(rows), hc)
+            ops.causal_conv_ragged(hn, tail, taps_w, d_rent, d_ent, hc)  # one tap: no tail, h * (1 + w)
 
         ops.embedding_f32(d_tok, self.w["embed"], x)
         pt = self.kv.page_table
@@ -495,11 +490,6 @@ class RaggedEngine:
         logits = logits_out[:nw] if logits_out is not None else torch.empty(nw, vp, dtype=E, device=dev)
         self._lin(hw, self.w["head"], logits)
         return logits
-
-    def _iota(self, rows: int) -> torch.Tensor:
-        if getattr(self, "_iota_t", None) is None or self._iota_t.numel() < rows:
-            self._iota_t = torch.arange(_ceil(rows, 1024), dtype=torch.int32, device=self.device)
-        return self._iota_t[:rows]
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()

@@ -51,6 +51,12 @@ def cfg_b():
                   width=48, vocab=53, taps=2)
 
 
+def cfg_c():
+    """one tap (the convolution sees the current input only), one head everywhere, chunk of one position, no scaling."""
+    return config([(attn(heads=1, kv=1, dim=8, vdim=8, chunk=1, rot_dims=2, scale=1.0, scaling=False), 32),
+                   (mlstm(heads=1, dim=4, vdim=4, cap=2.0), 0)], width=16, vocab=19, taps=1)
+
+
 def build(cfg, dtype, seed=0, max_batch=4, max_seq_len=256, pool=None, page_size=4):
     from dli_b200 import sokevik
     from dli_b200.ragged_engine import RaggedEngine
@@ -93,7 +99,7 @@ def run_schedule(eng, toks, cuts):
 TOL32, TOL16 = 2e-4, 0.08
 
 
-@pytest.mark.parametrize("make", [cfg_a, cfg_b])
+@pytest.mark.parametrize("make", [cfg_a, cfg_b, cfg_c])
 def test_whole_prompt_float32_matches_oracle_at_every_position(make):
     cfg = make()
     eng, sd = build(cfg, torch.float32)
@@ -115,7 +121,7 @@ def test_residual_stream_after_every_layer():
         assert (got.double().cpu() - ref).abs().max() < 1e-4 * ref.abs().max()
 
 
-@pytest.mark.parametrize("make", [cfg_a, cfg_b])
+@pytest.mark.parametrize("make", [cfg_a, cfg_b, cfg_c])
 @pytest.mark.parametrize("cuts", [[], [1, 1, 2], [2, 2, 3, 5, 7, 11], [17, 2, 16, 3], [30]])
 def test_portions_and_decoding_float32(make, cuts):
     """Token by token from the first token; portions of 2..; a prompt then decoding across several chunk edges."""
