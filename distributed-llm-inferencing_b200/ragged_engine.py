@@ -496,7 +496,7 @@ class RaggedEngine:
     def generate(self, input_ids: torch.Tensor, max_length: int, do_sample: bool = False, temperature: float = 0.8,
                  top_k: int = 50, top_p: float = 0.95, seed: int = 0, deadline: Optional[float] = None,
                  on_tokens=None, **_):
-        """ShardEngine.generate's contract (int [B, T] prompts -> int64 [B, <= max_length] on the host, greedy or
+        """ShardEngine.generate's signature and behaviour (int [B, T] prompts -> int64 [B, <= max_length] on the host, greedy or
         the sampling call), run by the ragged scheduler: prompts go in portions beside the decoding rows."""
         import time as _time
 

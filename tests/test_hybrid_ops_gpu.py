@@ -271,7 +271,7 @@ def mlstm_oracle(q, k, v, g, ig, fg, m, ib, fb, nw, eps):
     return R.mlstm_mixer(h, P, "", m, eps)
 
 
-@pytest.mark.parametrize("dims", [(2, 48, 64), (3, 10, 40), (1, 130, 33)])
+@pytest.mark.parametrize("dims", [(2, 56, 96), (3, 10, 40), (1, 130, 33)])
 @pytest.mark.parametrize("cuts", [[90], [1] * 90, [2, 2, 31, 1, 1, 40, 13], [70, 20], [300]])
 @pytest.mark.parametrize("blocked", [False, True, "parallel"])
 def test_mlstm_portions_and_dirty_slots(dims, cuts, blocked):
