@@ -68,7 +68,20 @@ SIGNATURES = {
     "dli_gemv_argmax_bf16": (_i, [_vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "dli_sample_bf16": (_i, [_vp, _i, _vp, _i, _i, _f, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
     "dli_decode_advance": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "dli_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "dli_residual_add2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dli_concat_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dli_rows_bias_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dli_latent_prep": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp,
+                             _i, _i, _vp]),
+    "dli_latent_q_absorb": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "dli_latent_v_up": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "dli_conv1d_act_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "dli_ssm_scan_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
+    "dli_gated_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _vp]),
+    "dli_moe_route": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "dli_moe_act": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _i, _f, _f, _i, _i, _vp]),
     "dli_scalar_rmsnorm_f32": (_i, [_vp, _vp, _i, _i, _f, _f, _vp]),
     "dli_postnorm_add_norm": (_i, [_vp, _vp, _vp, _i, _i, _f, _f, _f, _i, _vp]),
     "dli_causal_conv_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -79,7 +92,7 @@ SIGNATURES = {
     "dli_attn_prep_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                   _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "dli_attn_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
-                             _i, _vp, _vp, _i, _vp]),
+                             _i, _vp, _vp, _i, _i, _vp]),
     "dli_attn_ragged_tc_supported": (_i, [_i, _i, _i]),
     "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
                                 _i, _vp, _vp, _vp]),

@@ -32,6 +32,9 @@ SOURCES = [
     "ragged_rows.cu",
     "attn_ragged.cu",
     "mlstm.cu",
+    "latent_attn.cu",
+    "mamba2.cu",
+    "moe.cu",
 ]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

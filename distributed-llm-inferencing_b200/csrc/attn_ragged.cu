@@ -113,6 +113,8 @@ struct AttnRun {
   int ldp, g_off;           // gate column of the packed projection row, g_off < 0: no gate
   const float* cos_v;       // [positions, V/2] or NULL: turn the output back
   const float* sin_v;
+  int ldv;                  // elements between the value rows of consecutive positions (V; the key size when the
+                            // values are the leading part of the key rows of one shared pool)
 };
 
 // q (shared, fp32) . k row (global): 16-byte loads where the row allows them
@@ -206,7 +208,7 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     if (pv_active) {
       for (int jj = my_group; jj < cnt; jj += groups) {
         const int jk = j0 + jj;
-        const E* vr = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.V;
+        const E* vr = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.ldv;
         const float wj = p[jj];
 #pragma unroll
         for (int i = 0; i < kAttnMaxVPerThread; ++i) {
@@ -483,15 +485,17 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
-                    int g_off, const float* cos_v, const float* sin_v, int dt, dli_stream_t stream) {
+                    int g_off, const float* cos_v, const float* sin_v, int ldv, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && row_ent && ent && page_table, "dli_attn_ragged: null pointer");
+  DLI_CHECK_ARG(ldv == 0 || ldv >= V, "dli_attn_ragged: value row stride %d is below the value size %d", ldv, V);
   DLI_CHECK_ARG(g_off < 0 || proj, "dli_attn_ragged: a gate needs the projection rows");
   DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0 && V % 2 == 0 && V <= kAttnThreads * kAttnMaxVPerThread,
                 "dli_attn_ragged: H=%d G=%d D=%d V=%d (H %% G == 0, V even and <= %d)", H, G, D, V,
                 kAttnThreads * kAttnMaxVPerThread);
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
-  AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v};
+  AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v,
+            ldv ? ldv : V};
   const int groups = V >= kAttnThreads ? 1 : kAttnThreads / V;
   const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
   DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
@@ -516,7 +520,7 @@ int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cac
   if (!dli_attn_ragged_tc_supported(D, V, 0))
     return dli::fail(DLI_ERR_UNSUPPORTED, "dli_attn_ragged_tc: key size %d with value size %d has no tensor-core tile", D, V);
   if (n_tiles <= 0) return DLI_OK;
-  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v};
+  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v, V};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 64 && V == 64) return launch_ragged_tc<64, 64>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
   if (D == 128 && V == 128) return launch_ragged_tc<128, 128>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);

@@ -1,0 +1,226 @@
+// Latent attention for a RAGGED step: queries and keys/values both pass through a low-rank latent, and only the
+// key/value latent c [K] (RMS-normed) and one rotated key part k_r [R] shared by all heads are cached per position,
+// as one row [c | k_r] of a paged pool [pages, 1, page_size, K + R].
+//
+// With the per-head up-projections k_h = U_k[h] c and v_h = U_v[h] c the score of head h is
+//   q_n . (U_k[h] c) + q_r . k_r = (U_k[h]^T q_n) . c + q_r . k_r,
+// and the head's output is U_v[h] (sum_j p_j c_j).  So attention runs over the cached rows themselves, as ONE
+// key/value head shared by all query heads, with key size K + R and value = the first K entries of the key row
+// (dli_attn_ragged with ldv = K + R):
+//   dli_latent_prep      c_q = rmsnorm(W_dq h) -> operand of the query up-projection; c, rotated k_r -> the pool
+//   dli_latent_q_absorb  q~[h] = [U_k[h]^T q_n[h] | rot(q_r[h])] -> fp32 query rows of size K + R
+//   dli_latent_v_up      out[h] = (U_v[h] o~[h]) * sigmoid(gate[h])   with o~ the attention output in the latent
+// Rotation: interleaved pairs (2i, 2i+1) from a host-made fp32 cos/sin table [positions, R/2].  Norms, rotation and
+// the absorbed queries are fp32; E (bf16 or float) is the element type of projections and the pool.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dli {
+
+template <typename E> __device__ __forceinline__ float l_to_f(E v);
+template <> __device__ __forceinline__ float l_to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float l_to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename E> __device__ __forceinline__ E l_from_f(float v);
+template <> __device__ __forceinline__ float l_from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 l_from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float l_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+struct LatentPrep {
+  const int32_t* row_ent;
+  const int32_t* ent;
+  const int32_t* page_table;
+  int max_pages, page_size;
+  int Q, K, R;              // query latent size, key/value latent size, rotated key size
+  int ldp, q_off, kv_off;   // packed projection row: stride, column of the query latent, of [kv latent | k_r]
+  const float* qn;          // [Q] weight of the query latent's norm
+  const float* kn;          // [K] weight of the key/value latent's norm
+  float eps;
+  const float* cos_t;       // [positions, R/2]
+  const float* sin_t;
+};
+
+// One CTA per row.
+template <typename E>
+__global__ void __launch_bounds__(256)
+latent_prep_kernel(const E* __restrict__ proj, E* __restrict__ cq, E* __restrict__ pool, LatentPrep a) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[a.row_ent[row]];
+  const int pos = e.w + (row - e.y);
+  const size_t page = a.page_table[(size_t)e.x * a.max_pages + pos / a.page_size];
+  E* dst = pool + (page * a.page_size + pos % a.page_size) * (size_t)(a.K + a.R);
+  const E* pr = proj + (size_t)row * a.ldp;
+  float ss = 0.f;
+  for (int c = tid; c < a.Q; c += blockDim.x) { const float v = l_to_f(pr[a.q_off + c]); ss += v * v; }
+  ss = l_block_sum(ss, red);
+  float r = 1.f / sqrtf(ss / a.Q + a.eps);
+  for (int c = tid; c < a.Q; c += blockDim.x) cq[(size_t)row * a.Q + c] = l_from_f<E>(l_to_f(pr[a.q_off + c]) * r * a.qn[c]);
+  ss = 0.f;
+  for (int c = tid; c < a.K; c += blockDim.x) { const float v = l_to_f(pr[a.kv_off + c]); ss += v * v; }
+  ss = l_block_sum(ss, red);
+  r = 1.f / sqrtf(ss / a.K + a.eps);
+  for (int c = tid; c < a.K; c += blockDim.x) dst[c] = l_from_f<E>(l_to_f(pr[a.kv_off + c]) * r * a.kn[c]);
+  for (int i = tid; i < a.R / 2; i += blockDim.x) {
+    const float u = l_to_f(pr[a.kv_off + a.K + 2 * i]), v = l_to_f(pr[a.kv_off + a.K + 2 * i + 1]);
+    const float c = a.cos_t[(size_t)pos * (a.R / 2) + i], s = a.sin_t[(size_t)pos * (a.R / 2) + i];
+    dst[a.K + 2 * i] = l_from_f<E>(u * c - v * s);
+    dst[a.K + 2 * i + 1] = l_from_f<E>(v * c + u * s);
+  }
+}
+
+constexpr int kLatRows = 8;  // rows of a step that share one pass over a head's up-projection
+
+// qbuf[row, h, 0:K] = sum_d q[row, h, d] * uk[h, d, :],  qbuf[row, h, K:K+R] = rot(q[row, h, D:D+R], pos).
+// Grid (row tiles, heads); threads across the K outputs, the head's D query entries of the tile's rows in shared memory.
+template <typename E>
+__global__ void __launch_bounds__(256)
+latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float* __restrict__ qbuf,
+                       const int32_t* __restrict__ row_ent, const int32_t* __restrict__ ent, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, int rows, int H, int D, int R, int K) {
+  extern __shared__ float qs[];  // [kLatRows][D]
+  pdl_wait();
+  pdl_trigger();
+  const int r0 = blockIdx.x * kLatRows, h = blockIdx.y, tid = threadIdx.x;
+  const int nr = min(kLatRows, rows - r0);
+  for (int i = tid; i < kLatRows * D; i += blockDim.x) {
+    const int r = i / D, d = i - r * D;
+    qs[i] = r < nr ? l_to_f(q[((size_t)(r0 + r) * H + h) * (D + R) + d]) : 0.f;
+  }
+  __syncthreads();
+  const E* w = uk + (size_t)h * D * K;
+  for (int k = tid; k < K; k += blockDim.x) {
+    float acc[kLatRows];
+#pragma unroll
+    for (int r = 0; r < kLatRows; ++r) acc[r] = 0.f;
+    for (int d = 0; d < D; ++d) {
+      const float wv = l_to_f(w[(size_t)d * K + k]);
+#pragma unroll
+      for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(qs[r * D + d], wv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kLatRows; ++r)
+      if (r < nr) qbuf[((size_t)(r0 + r) * H + h) * (K + R) + k] = acc[r];
+  }
+  for (int i = tid; i < nr * (R / 2); i += blockDim.x) {
+    const int r = i / (R / 2), p = i - r * (R / 2);
+    const int row = r0 + r;
+    const int4 e = reinterpret_cast<const int4*>(ent)[row_ent[row]];
+    const int pos = e.w + (row - e.y);
+    const E* src = q + ((size_t)row * H + h) * (D + R) + D;
+    const float u = l_to_f(src[2 * p]), v = l_to_f(src[2 * p + 1]);
+    const float c = cos_t[(size_t)pos * (R / 2) + p], s = sin_t[(size_t)pos * (R / 2) + p];
+    float* dst = qbuf + ((size_t)row * H + h) * (K + R) + K;
+    dst[2 * p] = u * c - v * s;
+    dst[2 * p + 1] = v * c + u * s;
+  }
+}
+
+// out[row, h*V + v] = (sum_k uv[h, v, k] * o[row, h, k]) * sigmoid(proj[row, g_off + h*V + v])   (g_off < 0: no gate)
+// Grid (row tiles, heads); one warp per output v, lanes across K, the tile's latent outputs in shared memory.
+template <typename E>
+__global__ void __launch_bounds__(256)
+latent_v_up_kernel(const E* __restrict__ o, const E* __restrict__ uv, const E* __restrict__ proj, E* __restrict__ out,
+                   int rows, int H, int V, int K, int ldp, int g_off) {
+  extern __shared__ float os[];  // [kLatRows][K]
+  pdl_wait();
+  pdl_trigger();
+  const int r0 = blockIdx.x * kLatRows, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nr = min(kLatRows, rows - r0), nw = blockDim.x >> 5;
+  for (int i = tid; i < kLatRows * K; i += blockDim.x) {
+    const int r = i / K, k = i - r * K;
+    os[i] = r < nr ? l_to_f(o[((size_t)(r0 + r) * H + h) * K + k]) : 0.f;
+  }
+  __syncthreads();
+  for (int v = warp; v < V; v += nw) {
+    const E* w = uv + ((size_t)h * V + v) * K;
+    float acc[kLatRows];
+#pragma unroll
+    for (int r = 0; r < kLatRows; ++r) acc[r] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float wv = l_to_f(w[k]);
+#pragma unroll
+      for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(os[r * K + k], wv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kLatRows; ++r) acc[r] = warp_sum(acc[r]);
+    if (lane < nr) {
+      float val = 0.f;
+#pragma unroll
+      for (int r = 0; r < kLatRows; ++r) if (r == lane) val = acc[r];
+      const size_t row = r0 + lane;
+      if (g_off >= 0) val *= 1.f / (1.f + expf(-l_to_f(proj[row * ldp + g_off + h * V + v])));
+      out[(row * H + h) * V + v] = l_from_f<E>(val);
+    }
+  }
+}
+
+}  // namespace dli
+
+using namespace dli;
+
+extern "C" {
+
+int dli_latent_prep(const void* proj, void* cq, void* pool, const int32_t* row_ent, const int32_t* ent,
+                    const int32_t* page_table, int max_pages, int page_size, int rows, int Q, int K, int R, int ldp,
+                    int q_off, int kv_off, const float* q_norm, const float* kv_norm, float eps, const float* cos_t,
+                    const float* sin_t, int table_len, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(proj && cq && pool && row_ent && ent && page_table && q_norm && kv_norm, "dli_latent_prep: null pointer");
+  DLI_CHECK_ARG(Q > 0 && K > 0 && R >= 0 && R % 2 == 0 && (R == 0 || (cos_t && sin_t && table_len > 0)),
+                "dli_latent_prep: Q=%d K=%d R=%d (R even, with a rotation table)", Q, K, R);
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_latent_prep: ent must be 16-byte aligned");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  LatentPrep a{row_ent, ent, page_table, max_pages, page_size, Q, K, R, ldp, q_off, kv_off, q_norm, kv_norm, eps, cos_t, sin_t};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("latent_prep", latent_prep_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)proj, (bf16*)cq, (bf16*)pool, a);
+  else DLI_LAUNCH("latent_prep", latent_prep_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)proj, (float*)cq, (float*)pool, a);
+  return DLI_OK;
+}
+
+int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_t* row_ent, const int32_t* ent,
+                        const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int dt,
+                        dli_stream_t stream) {
+  DLI_CHECK_ARG(q && uk && qbuf && row_ent && ent, "dli_latent_q_absorb: null pointer");
+  DLI_CHECK_ARG(H > 0 && D > 0 && K > 0 && R >= 0 && R % 2 == 0 && (R == 0 || (cos_t && sin_t)) &&
+                    (size_t)kLatRows * D * sizeof(float) <= 48 * 1024,
+                "dli_latent_q_absorb: H=%d D=%d R=%d K=%d", H, D, R, K);
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid((rows + kLatRows - 1) / kLatRows, H);
+  const size_t smem = (size_t)kLatRows * D * sizeof(float);
+  const int th = K >= 256 ? 256 : 128;
+  if (dt == 0) DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<bf16>, grid, dim3(th), smem, s, (const bf16*)q, (const bf16*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K);
+  else DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<float>, grid, dim3(th), smem, s, (const float*)q, (const float*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K);
+  return DLI_OK;
+}
+
+int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, int rows, int H, int V, int K, int ldp,
+                    int g_off, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(o && uv && out && (g_off < 0 || proj), "dli_latent_v_up: null pointer");
+  DLI_CHECK_ARG(H > 0 && V > 0 && K > 0 && (size_t)kLatRows * K * sizeof(float) <= 48 * 1024,
+                "dli_latent_v_up: H=%d V=%d K=%d (K <= %d)", H, V, K, 48 * 1024 / (kLatRows * 4));
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid((rows + kLatRows - 1) / kLatRows, H);
+  const size_t smem = (size_t)kLatRows * K * sizeof(float);
+  if (dt == 0) DLI_LAUNCH("latent_v_up", latent_v_up_kernel<bf16>, grid, dim3(256), smem, s, (const bf16*)o, (const bf16*)uv, (const bf16*)proj, (bf16*)out, rows, H, V, K, ldp, g_off);
+  else DLI_LAUNCH("latent_v_up", latent_v_up_kernel<float>, grid, dim3(256), smem, s, (const float*)o, (const float*)uv, (const float*)proj, (float*)out, rows, H, V, K, ldp, g_off);
+  return DLI_OK;
+}
+
+}  // extern "C"

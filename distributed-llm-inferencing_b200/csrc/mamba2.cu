@@ -1,0 +1,241 @@
+// Selective state-space mixer (Mamba-2 form) for a RAGGED step.  The input projection's row is laid out as
+// [z: H*V | x: H*V | B: G*N | C: G*N | dt: H].  Three kernels:
+//   dli_conv1d_act_ragged   causal per-channel convolution over time of a block of projection columns (x, B, C),
+//                           with bias and SiLU, reading the sequence's last taps-1 inputs from its state slot and
+//                           advancing them -> fp32 rows
+//   dli_ssm_scan_ragged     per head h (group g = h / (H/G)):  dt_t = softplus(dt_t + dt_bias_h),
+//                           S_t = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T   (S: N x V, fp32, per state slot)
+//                           y_t = S_t^T C_t + D_h x_t
+//   dli_gated_group_rmsnorm y * silu(z), RMS norm in groups, times a weight per channel -> the out-projection's operand
+// Everything that enters the recurrence after the convolution is fp32.  An entry whose first position is 0 starts
+// from a zero state and a zero convolution history whatever its slot held before.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dli {
+
+template <typename E> __device__ __forceinline__ float m_to_f(E v);
+template <> __device__ __forceinline__ float m_to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float m_to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename E> __device__ __forceinline__ E m_from_f(float v);
+template <> __device__ __forceinline__ float m_from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 m_from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float m_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// out[row, c] = act(bias[c] + sum_j w[c, j] * in[t - taps + 1 + j, c]); in = columns [off, off + C) of proj.
+// Inputs before the entry's first row come from tail [slots, taps-1, C] (oldest first), zeros before position 0.
+template <typename E>
+__global__ void __launch_bounds__(256)
+conv1d_act_kernel(const E* __restrict__ proj, const float* __restrict__ tail, const float* __restrict__ w,
+                  const float* __restrict__ bias, const int32_t* __restrict__ row_ent, const int32_t* __restrict__ ent,
+                  float* __restrict__ out, int C, int taps, int ldp, int off, int act) {
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  const int4 e = reinterpret_cast<const int4*>(ent)[row_ent[row]];  // slot, row0, n, start
+  const int back = row - e.y, pos = e.w + back;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int dist = taps - 1 - j;
+      if (pos - dist < 0) continue;
+      float v;
+      if (dist <= back) v = m_to_f(proj[(size_t)(row - dist) * ldp + off + c]);
+      else v = tail[((size_t)e.x * (taps - 1) + (taps - 1 - (dist - back))) * C + c];
+      acc = fmaf(w[(size_t)c * taps + j], v, acc);
+    }
+    if (act == 1) acc = acc / (1.f + expf(-acc));
+    out[(size_t)row * C + c] = acc;
+  }
+}
+
+// After the convolution: the slot's tail becomes the last taps-1 inputs of the sequence.
+template <typename E>
+__global__ void __launch_bounds__(256)
+conv1d_tail_kernel(const E* __restrict__ proj, float* __restrict__ tail, const int32_t* __restrict__ ent, int C, int taps,
+                   int ldp, int off) {
+  pdl_wait();
+  pdl_trigger();
+  const int4 e = reinterpret_cast<const int4*>(ent)[blockIdx.x];
+  const int keep = taps - 1, end = e.w + e.z;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float* t = tail + (size_t)e.x * keep * C + c;
+    for (int i = 0; i < keep; ++i) {  // ascending: slot i reads old slot i + n (n >= 1), never one already written
+      const int p = end - keep + i;
+      float v = 0.f;
+      if (p >= e.w) v = m_to_f(proj[(size_t)(e.y + p - e.w) * ldp + off + c]);
+      else if (p >= 0) v = t[(size_t)(keep - (e.w - p)) * C];
+      t[(size_t)i * C] = v;
+    }
+  }
+}
+
+struct SsmRun {
+  const int32_t* ent;
+  int H, V, N, G;
+  int ldx;                  // row stride of xbc (fp32 [rows, H*V + 2*G*N]: x | B | C)
+  int ldp, dt_off;          // the projection row's stride and the column of dt
+  const float* dt_bias;     // [H]
+  const float* a_log;       // [H]
+  const float* d_skip;      // [H]
+  int np;                   // threads that share one value column (a power of two <= 32); each holds N/np state rows
+  int vc;                   // value columns per CTA
+};
+
+constexpr int kSsmMaxPerThread = 16;
+
+// Grid (entries, heads, ceil(V / vc)); the CTA walks the entry's rows in order with its part of the state in
+// registers: thread (v, p) holds S[n, v] for n = p, p + np, ...
+template <typename E>
+__global__ void __launch_bounds__(256)
+ssm_scan_kernel(const float* __restrict__ xbc, const E* __restrict__ proj, float* __restrict__ S, float* __restrict__ y,
+                SsmRun a) {
+  pdl_wait();
+  pdl_trigger();
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[blockIdx.x];  // slot, row0, n, start
+  const int h = blockIdx.y, g = h / (a.H / a.G);
+  const int p = threadIdx.x % a.np, vl = threadIdx.x / a.np;
+  const int v = blockIdx.z * a.vc + vl;
+  const bool active = vl < a.vc && v < a.V;
+  const int inner = a.H * a.V;
+  float s[kSsmMaxPerThread];
+  float* Sp = S + (((size_t)e.x * a.H + h) * a.N) * a.V;
+#pragma unroll
+  for (int i = 0; i < kSsmMaxPerThread; ++i) {
+    const int n = p + i * a.np;
+    s[i] = (active && n < a.N && e.w > 0) ? Sp[(size_t)n * a.V + v] : 0.f;
+  }
+  const float na = -expf(a.a_log[h]), db = a.dt_bias[h], dk = a.d_skip[h];
+  for (int t = 0; t < e.z; ++t) {
+    const size_t row = (size_t)e.y + t;
+    const float* xr = xbc + row * a.ldx;
+    const float draw = m_to_f(proj[row * a.ldp + a.dt_off + h]) + db;
+    const float dt = draw > 20.f ? draw : log1pf(expf(draw));
+    const float decay = expf(na * dt);
+    const float xv = active ? xr[h * a.V + v] : 0.f;
+    const float* Bt = xr + inner + g * a.N;
+    const float* Ct = xr + inner + a.G * a.N + g * a.N;
+    const float bx = dt * xv;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kSsmMaxPerThread; ++i) {
+      const int n = p + i * a.np;
+      if (n < a.N) {
+        s[i] = fmaf(decay, s[i], Bt[n] * bx);
+        acc = fmaf(s[i], Ct[n], acc);
+      }
+    }
+    for (int o = a.np >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (active && p == 0) y[row * inner + h * a.V + v] = acc + dk * xv;
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < kSsmMaxPerThread; ++i) {
+      const int n = p + i * a.np;
+      if (n < a.N) Sp[(size_t)n * a.V + v] = s[i];
+    }
+  }
+}
+
+// out[row] = groupnorm(y[row] * silu(z[row])) * w; z = columns [z_off, z_off + d) of proj.
+template <typename E>
+__global__ void __launch_bounds__(1024)
+gated_group_rmsnorm_kernel(const float* __restrict__ y, const E* __restrict__ proj, const float* __restrict__ w,
+                           E* __restrict__ out, int d, int groups, float eps, int ldp, int z_off) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  const int gd = d / groups;
+  for (int g = 0; g < groups; ++g) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < gd; c += blockDim.x) {
+      const float z = m_to_f(proj[row * ldp + z_off + g * gd + c]);
+      const float v = y[row * d + g * gd + c] * (z / (1.f + expf(-z)));
+      ss += v * v;
+    }
+    ss = m_block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / gd + eps);
+    for (int c = threadIdx.x; c < gd; c += blockDim.x) {
+      const float z = m_to_f(proj[row * ldp + z_off + g * gd + c]);
+      const float v = y[row * d + g * gd + c] * (z / (1.f + expf(-z)));
+      out[row * d + g * gd + c] = m_from_f<E>(v * r * w[g * gd + c]);
+    }
+  }
+}
+
+}  // namespace dli
+
+using namespace dli;
+
+extern "C" {
+
+int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const float* bias, const int32_t* row_ent,
+                          const int32_t* ent, float* out, int rows, int n_ent, int C, int taps, int ldp, int off, int act,
+                          int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(proj && w && row_ent && ent && out && C > 0 && taps >= 1 && ldp >= off + C && off >= 0,
+                "dli_conv1d_act_ragged: null pointer or bad shape");
+  DLI_CHECK_ARG(tail || taps == 1, "dli_conv1d_act_ragged: taps > 1 needs a tail state");
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_conv1d_act_ragged: ent must be 16-byte aligned");
+  DLI_CHECK_ARG(act == 0 || act == 1, "dli_conv1d_act_ragged: activation %d (0 = none, 1 = silu)", act);
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("conv1d_act", conv1d_act_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
+  else DLI_LAUNCH("conv1d_act", conv1d_act_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
+  if (taps > 1) {
+    if (dt == 0) DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<bf16>, dim3(n_ent), dim3(256), 0, s, (const bf16*)proj, tail, ent, C, taps, ldp, off);
+    else DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<float>, dim3(n_ent), dim3(256), 0, s, (const float*)proj, tail, ent, C, taps, ldp, off);
+  }
+  return DLI_OK;
+}
+
+int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, const int32_t* ent, int n_ent, int H, int V,
+                        int N, int G, int ldp, int dt_off, const float* dt_bias, const float* a_log, const float* d_skip,
+                        int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(xbc && proj && S && y && ent && dt_bias && a_log && d_skip, "dli_ssm_scan_ragged: null pointer");
+  DLI_CHECK_ARG(H > 0 && V > 0 && N > 0 && G > 0 && H % G == 0 && N <= 32 * kSsmMaxPerThread,
+                "dli_ssm_scan_ragged: H=%d V=%d N=%d G=%d (H %% G == 0, N <= %d)", H, V, N, G, 32 * kSsmMaxPerThread);
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_ssm_scan_ragged: ent must be 16-byte aligned");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (n_ent <= 0) return DLI_OK;
+  int np = 1;
+  while (np * kSsmMaxPerThread < N) np <<= 1;
+  // few value columns per CTA: a scan is one dependent chain per entry and head, so the columns are what spreads it
+  // over the SMs
+  int vc = 256 / np;
+  while (vc > 8 && (long)n_ent * H * ((V + vc - 1) / vc) < 2L * sm_count_cached()) vc >>= 1;
+  if (vc > V) vc = V;
+  const int threads = ((vc * np + 31) / 32) * 32;
+  SsmRun a{ent, H, V, N, G, H * V + 2 * G * N, ldp, dt_off, dt_bias, a_log, d_skip, np, vc};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(n_ent, H, (V + vc - 1) / vc);
+  if (dt == 0) DLI_LAUNCH("ssm_scan", ssm_scan_kernel<bf16>, grid, dim3(threads), 0, s, xbc, (const bf16*)proj, S, y, a);
+  else DLI_LAUNCH("ssm_scan", ssm_scan_kernel<float>, grid, dim3(threads), 0, s, xbc, (const float*)proj, S, y, a);
+  return DLI_OK;
+}
+
+int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, void* out, int rows, int d, int groups,
+                            float eps, int ldp, int z_off, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(y && proj && w && out && d > 0 && groups > 0 && d % groups == 0 && ldp >= z_off + d && z_off >= 0,
+                "dli_gated_group_rmsnorm: null pointer, or size %d is not a multiple of %d groups", d, groups);
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("gated_group_rmsnorm", gated_group_rmsnorm_kernel<bf16>, dim3(rows), dim3(256), 0, s, y, (const bf16*)proj, w, (bf16*)out, d, groups, eps, ldp, z_off);
+  else DLI_LAUNCH("gated_group_rmsnorm", gated_group_rmsnorm_kernel<float>, dim3(rows), dim3(256), 0, s, y, (const float*)proj, w, (float*)out, d, groups, eps, ldp, z_off);
+  return DLI_OK;
+}
+
+}  // extern "C"

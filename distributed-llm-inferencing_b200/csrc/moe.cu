@@ -1,0 +1,168 @@
+// Mixture-of-experts feed-forward for a RAGGED step: the router and the expert activation.
+//
+//   dli_moe_route   logits z = W_r h (fp32), scores s = softmax(z) over all router outputs; the `top` outputs with
+//                   the largest s + correction are chosen; their weights are s / (sum of the chosen s + 1e-20).
+//                   The last n_identity router outputs are experts that return their input: their weights are
+//                   summed into idw[row].  Written: the dense weight row wts[row, 0 .. n_real) (0 for experts that
+//                   were not chosen), idw[row], and the choice itself (sel_idx / sel_w [row, top]).
+//   dli_moe_act     the experts' activation on the stacked gate/up projection of all experts:
+//                   g = min(g, limit), u = clamp(u, -limit, limit), a = g * sigmoid(alpha g) * (u + 1), times the
+//                   expert's routing weight, so that ONE down projection over the concatenated experts is the
+//                   weighted sum of their outputs.  A shared expert (its own size and limit, weight 1) is the last
+//                   block.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dli {
+
+template <typename E> __device__ __forceinline__ float x_to_f(E v);
+template <> __device__ __forceinline__ float x_to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float x_to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename E> __device__ __forceinline__ E x_from_f(float v);
+template <> __device__ __forceinline__ float x_from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 x_from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// One CTA per row: a warp per router output for the logits, then one warp does the softmax and the choice.
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
+                 float* __restrict__ wts, float* __restrict__ idw, int32_t* __restrict__ sel_idx,
+                 float* __restrict__ sel_w, int d, int n_out, int n_real, int top) {
+  extern __shared__ float zs[];  // [n_out] scores, [n_out] choice scores
+  float* cs = zs + n_out;
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* hr = h + row * d;
+  for (int o = warp; o < n_out; o += nw) {
+    const float* w = wr + (size_t)o * d;
+    float acc = 0.f;
+    for (int c = lane; c < d; c += 32) acc = fmaf(hr[c], w[c], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) zs[o] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int o = lane; o < n_out; o += 32) mx = fmaxf(mx, zs[o]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int o = lane; o < n_out; o += 32) sum += expf(zs[o] - mx);
+  sum = warp_sum(sum);
+  for (int o = lane; o < n_out; o += 32) {
+    const float s = expf(zs[o] - mx) / sum;
+    zs[o] = s;
+    cs[o] = s + (corr ? corr[o] : 0.f);
+    if (o < n_real) wts[row * n_real + o] = 0.f;
+  }
+  __syncwarp();
+  // the `top` largest choice scores, one at a time (lowest index wins a tie)
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int o = lane; o < n_out; o += 32) {
+      const float c = cs[o];
+      if (c > best) { best = c; bi = o; }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) {
+      cs[bi] = -INFINITY;
+      sel_idx[row * top + k] = bi;
+    }
+    chosen_sum += zs[bi];
+    __syncwarp();
+  }
+  const float inv = 1.f / (chosen_sum + 1e-20f);
+  if (lane == 0) {
+    float ident = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int o = sel_idx[row * top + k];
+      const float w = zs[o] * inv;
+      sel_w[row * top + k] = w;
+      if (o < n_real) wts[row * n_real + o] = w;
+      else ident += w;
+    }
+    idw[row] = ident;
+  }
+}
+
+struct MoeAct {
+  int n_exp, ff;            // routed experts and their size; columns [e*2*ff, +ff) gate, [e*2*ff + ff, +ff) up
+  float limit;
+  int ff_s;                 // shared expert's size (0: none), its gate/up follow the routed experts'
+  float limit_s;
+  float alpha;              // g * sigmoid(alpha * g)
+  int ld;                   // row stride of gu
+};
+
+// act[row, e*ff + f] and act[row, n_exp*ff + f] (shared); one CTA per row.
+template <typename E>
+__global__ void __launch_bounds__(256)
+moe_act_kernel(const E* __restrict__ gu, const float* __restrict__ wts, E* __restrict__ act, MoeAct a) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  const E* g = gu + row * a.ld;
+  const int F = a.n_exp * a.ff + a.ff_s;
+  E* out = act + row * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    float gv, uv, lim, wt;
+    if (i < a.n_exp * a.ff) {
+      const int e = i / a.ff, f = i - e * a.ff;
+      wt = wts[row * a.n_exp + e];
+      if (wt == 0.f) { out[i] = x_from_f<E>(0.f); continue; }
+      gv = x_to_f(g[(size_t)e * 2 * a.ff + f]);
+      uv = x_to_f(g[(size_t)e * 2 * a.ff + a.ff + f]);
+      lim = a.limit;
+    } else {
+      const int f = i - a.n_exp * a.ff;
+      wt = 1.f;
+      gv = x_to_f(g[(size_t)a.n_exp * 2 * a.ff + f]);
+      uv = x_to_f(g[(size_t)a.n_exp * 2 * a.ff + a.ff_s + f]);
+      lim = a.limit_s;
+    }
+    gv = fminf(gv, lim);
+    uv = fminf(fmaxf(uv, -lim), lim);
+    const float y = gv / (1.f + expf(-a.alpha * gv)) * (uv + 1.f);
+    out[i] = x_from_f<E>(y * wt);
+  }
+}
+
+}  // namespace dli
+
+using namespace dli;
+
+extern "C" {
+
+int dli_moe_route(const float* h, const float* w_router, const float* correction, float* wts, float* idw, int32_t* sel_idx,
+                  float* sel_w, int rows, int d, int n_out, int n_real, int top, dli_stream_t stream) {
+  DLI_CHECK_ARG(h && w_router && wts && idw && sel_idx && sel_w, "dli_moe_route: null pointer");
+  DLI_CHECK_ARG(d > 0 && n_out > 0 && n_real >= 0 && n_real <= n_out && top > 0 && top <= n_out && n_out <= 4096,
+                "dli_moe_route: %d router outputs (%d real experts), top %d", n_out, n_real, top);
+  if (rows <= 0) return DLI_OK;
+  DLI_LAUNCH("moe_route", moe_route_kernel, dim3(rows), dim3(256), (size_t)2 * n_out * sizeof(float),
+             static_cast<cudaStream_t>(stream), h, w_router, correction, wts, idw, sel_idx, sel_w, d, n_out, n_real, top);
+  return DLI_OK;
+}
+
+int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp, int ff, float limit, int ff_s,
+                float limit_s, float alpha, int ld, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(gu && act && (wts || n_exp == 0) && n_exp >= 0 && ff >= 0 && ff_s >= 0 && n_exp * ff + ff_s > 0 &&
+                    ld >= 2 * (n_exp * ff + ff_s),
+                "dli_moe_act: null pointer or bad shape");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, ld};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("moe_act", moe_act_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)gu, wts, (bf16*)act, a);
+  else DLI_LAUNCH("moe_act", moe_act_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)gu, wts, (float*)act, a);
+  return DLI_OK;
+}
+
+}  // extern "C"

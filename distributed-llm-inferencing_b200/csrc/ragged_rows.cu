@@ -34,13 +34,85 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // x[row] = table[ids[row]] as fp32 (the residual stream starts in fp32).
 template <typename E>
 __global__ void __launch_bounds__(1024)
-embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ table, float* __restrict__ x, int d, int vocab) {
+embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ table, float* __restrict__ x,
+                     float* __restrict__ x2, int d, int vocab, float scale) {
   pdl_wait();
   pdl_trigger();
   const size_t row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
-  for (int c = threadIdx.x; c < d; c += blockDim.x) x[row * d + c] = to_f(table[(size_t)id * d + c]);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = to_f(table[(size_t)id * d + c]) * scale;
+    x[row * d + c] = v;
+    if (x2) x2[row * d + c] = v;
+  }
+}
+
+// RMS norm in GROUPS with a weight per channel: the row is cut into `groups` equal consecutive parts, each divided
+// by its own sqrt(mean(part^2) + eps), the whole multiplied by w.  hn (fp32) and he (element type E) are both
+// optional outputs: a layer whose mixer reads the normed row through an fp32 convolution while its feed-forward
+// reads it as a GEMM operand wants both.
+template <typename E>
+__global__ void __launch_bounds__(1024)
+group_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ hn,
+                     E* __restrict__ he, int d, int groups, float eps) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const size_t o = (size_t)blockIdx.x * d;
+  const int gd = d / groups;
+  for (int g = 0; g < groups; ++g) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < gd; c += blockDim.x) { const float v = x[o + g * gd + c]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / gd + eps);
+    for (int c = threadIdx.x; c < gd; c += blockDim.x) {
+      const float v = x[o + g * gd + c] * r * w[g * gd + c];
+      if (hn) hn[o + g * gd + c] = v;
+      if (he) he[o + g * gd + c] = from_f<E>(v);
+    }
+  }
+}
+
+// x += y1 + y2 + a[row] * h: the residual add of a layer whose sublayers run side by side on one normed input
+// (y2, and a with h, optional; a[row] is the weight of the branches that pass their input through unchanged).
+template <typename E>
+__global__ void __launch_bounds__(256)
+residual_add2_kernel(float* __restrict__ x, const E* __restrict__ y1, const E* __restrict__ y2,
+                     const float* __restrict__ a, const float* __restrict__ h, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t o = (size_t)blockIdx.x * d;
+  const float aw = a ? a[blockIdx.x] : 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float v = to_f(y1[o + c]);
+    if (y2) v += to_f(y2[o + c]);
+    if (a) v += aw * h[o + c];
+    x[o + c] += v;
+  }
+}
+
+// out[row] = E([a[row] | b[row]]): two fp32 rows side by side as one GEMM operand.
+template <typename E>
+__global__ void __launch_bounds__(256)
+concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, E* __restrict__ out, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t r = blockIdx.x;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    out[r * 2 * d + c] = from_f<E>(a[r * d + c]);
+    out[r * 2 * d + d + c] = from_f<E>(b[r * d + c]);
+  }
+}
+
+// x[row] = y[row] + bias: a projection's output becomes the fp32 residual stream.
+template <typename E>
+__global__ void __launch_bounds__(256)
+rows_bias_f32_kernel(const E* __restrict__ y, const float* __restrict__ bias, float* __restrict__ x, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t o = (size_t)blockIdx.x * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) x[o + c] = to_f(y[o + c]) + (bias ? bias[c] : 0.f);
 }
 
 // hn = x / sqrt(mean(x^2) + eps) * g  with ONE weight g for the whole row.
@@ -303,14 +375,58 @@ static inline int row_threads(int rows, int d) { return (rows <= 64 && d >= 2048
 
 extern "C" {
 
-int dli_embedding_f32(const int32_t* ids, const void* table, float* x, int rows, int d, int vocab, int dt,
-                      dli_stream_t stream) {
+int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, int rows, int d, int vocab, float scale,
+                      int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(ids && table && x && d > 0 && vocab > 0, "dli_embedding_f32: null pointer or empty shape");
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, d, vocab);
-  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, d, vocab);
+  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, x2, d, vocab, scale);
+  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, x2, d, vocab, scale);
+  return DLI_OK;
+}
+
+int dli_group_rmsnorm(const float* x, const float* w, float* hn, void* he, int rows, int d, int groups, float eps, int dt,
+                      dli_stream_t stream) {
+  DLI_CHECK_ARG(x && w && (hn || he) && d > 0 && groups > 0 && d % groups == 0,
+                "dli_group_rmsnorm: null pointer, or width %d is not a multiple of %d groups", d, groups);
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int th = (rows <= 64 && d / groups >= 2048) ? 1024 : 256;
+  if (dt == 0) DLI_LAUNCH("group_rmsnorm", group_rmsnorm_kernel<bf16>, dim3(rows), dim3(th), 0, s, x, w, hn, (bf16*)he, d, groups, eps);
+  else DLI_LAUNCH("group_rmsnorm", group_rmsnorm_kernel<float>, dim3(rows), dim3(th), 0, s, x, w, hn, (float*)he, d, groups, eps);
+  return DLI_OK;
+}
+
+int dli_residual_add2(float* x, const void* y1, const void* y2, const float* a, const float* h, int rows, int d, int dt,
+                      dli_stream_t stream) {
+  DLI_CHECK_ARG(x && y1 && d > 0 && (!a || h), "dli_residual_add2: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("residual_add2", residual_add2_kernel<bf16>, dim3(rows), dim3(256), 0, s, x, (const bf16*)y1, (const bf16*)y2, a, h, d);
+  else DLI_LAUNCH("residual_add2", residual_add2_kernel<float>, dim3(rows), dim3(256), 0, s, x, (const float*)y1, (const float*)y2, a, h, d);
+  return DLI_OK;
+}
+
+int dli_concat_cast(const float* a, const float* b, void* out, int rows, int d, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(a && b && out && d > 0, "dli_concat_cast: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("concat_cast", concat_cast_kernel<bf16>, dim3(rows), dim3(256), 0, s, a, b, (bf16*)out, d);
+  else DLI_LAUNCH("concat_cast", concat_cast_kernel<float>, dim3(rows), dim3(256), 0, s, a, b, (float*)out, d);
+  return DLI_OK;
+}
+
+int dli_rows_bias_f32(const void* y, const float* bias, float* x, int rows, int d, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(y && x && d > 0, "dli_rows_bias_f32: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("rows_bias_f32", rows_bias_f32_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)y, bias, x, d);
+  else DLI_LAUNCH("rows_bias_f32", rows_bias_f32_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)y, bias, x, d);
   return DLI_OK;
 }
 

@@ -1,8 +1,9 @@
 """Model registry: which engine serves a model directory.
 
 config.json decides: `model_type` llama / mistral / gpt2 -> engine.ShardEngine (uniform stacks, Hugging Face tensor
-names); `architecture` Sokevik -> ragged_engine.RaggedEngine with the layer list of sokevik.py.  The worker, the
-trace replayer (bin/trace_run) and bench.py all come through here.
+names); `architecture` Sokevik or Togalorn -> ragged_engine.RaggedEngine with the layer list that sokevik.py /
+togalorn.py read from the configuration.  The worker, the trace replayer (bin/trace_run) and bench.py all come
+through here.
 """
 from __future__ import annotations
 
@@ -18,19 +19,38 @@ def read_config(path: str) -> dict:
         return json.load(f)
 
 
+# designs described layer by layer, served by RaggedEngine: architecture -> module with spec_from_config,
+# model_tensors and random_state_dict
+LAYERWISE = {"Sokevik": "sokevik", "Togalorn": "togalorn"}
+
+
 def family(cfg: dict) -> str:
-    if cfg.get("architecture") == "Sokevik":
-        return "sokevik"
+    if cfg.get("architecture") in LAYERWISE:
+        return LAYERWISE[cfg["architecture"]]
     if cfg.get("model_type") in ("llama", "mistral", "gpt2"):
         return "uniform"
     raise ValueError(f"unsupported model: model_type {cfg.get('model_type')!r}, architecture {cfg.get('architecture')!r} "
-                     "(llama, mistral, gpt2, Sokevik)")
+                     f"(llama, mistral, gpt2, {', '.join(LAYERWISE)})")
+
+
+def definition(cfg: dict):
+    """The module that defines a layer-by-layer design, None for the uniform stacks."""
+    fam = family(cfg)
+    if fam == "uniform":
+        return None
+    import importlib
+    return importlib.import_module("." + fam, __package__)
+
+
+def supports_float32(cfg: dict) -> bool:
+    """RaggedEngine has a true-fp32 mode; the uniform-stack engine is bf16 only."""
+    return family(cfg) != "uniform"
 
 
 def spec_from_config(cfg: dict):
-    if family(cfg) == "sokevik":
-        from .sokevik import spec_from_config as f
-        return f(cfg)
+    mod = definition(cfg)
+    if mod is not None:
+        return mod.spec_from_config(cfg)
     from .engine import ModelSpec
     return ModelSpec.from_hf_config(cfg)
 
@@ -55,13 +75,13 @@ def load_engine(path: str, device: str = "cuda:0", max_batch: int = 1, max_seq_l
     """A full-range engine with the directory's weights loaded."""
     cfg = read_config(path)
     spec = spec_from_config(cfg)
-    if family(cfg) == "sokevik":
-        from . import sokevik
+    mod = definition(cfg)
+    if mod is not None:
         from .ragged_engine import RaggedEngine
 
         eng = RaggedEngine(spec, device=device, max_batch=max_batch, max_seq_len=max_seq_len,
                            kv_pool_tokens=kv_pool_tokens, dtype=dtype)
-        eng.load_tensors(sokevik.model_tensors(spec, read_all_tensors(path)))
+        eng.load_tensors(mod.model_tensors(spec, read_all_tensors(path)))
         return eng
     if dtype != torch.bfloat16:
         raise ValueError("the uniform-stack engine runs in bfloat16 only")

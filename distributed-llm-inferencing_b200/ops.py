@@ -467,12 +467,43 @@ def _i32(*ts):
         _req(t, torch.int32)
 
 
-def embedding_f32(ids, table, out):
-    """ids int32 [rows]; table [V, d] bf16 / float -> out float32 [rows, d]."""
-    _i32(ids), _req(table, table.dtype), _f32(out)
-    _call("dli_embedding_f32", 1, _p(ids), _p(table), _p(out), ids.numel(), table.shape[1], table.shape[0], _dt(table),
-          _stream())
+def embedding_f32(ids, table, out, scale: float = 1.0, out2=None):
+    """ids int32 [rows]; table [V, d] bf16 / float -> out float32 [rows, d] = table[ids] * scale (out2: a second copy)."""
+    _i32(ids), _req(table, table.dtype), _f32(out, out2)
+    _call("dli_embedding_f32", 1, _p(ids), _p(table), _p(out), _p(out2), ids.numel(), table.shape[1], table.shape[0],
+          float(scale), _dt(table), _stream())
     return out
+
+
+def group_rmsnorm(x, w, groups: int, eps: float, hn=None, he=None):
+    """RMS norm of x float32 [rows, d] in `groups` equal parts, times w float32 [d] -> hn (float32) and / or he
+    (bf16 / float32)."""
+    _f32(x, w, hn)
+    if he is not None:
+        _req(he, he.dtype)
+    _call("dli_group_rmsnorm", 1, _p(x), _p(w), _p(hn), _p(he), x.shape[0], x.shape[1], int(groups), float(eps),
+          _dt(he) if he is not None else 1, _stream())
+
+
+def residual_add2(x, y1, y2=None, a=None, h=None):
+    """x += y1 + y2 + a[:, None] * h (x, a, h float32; y1, y2 in one element type)."""
+    _f32(x, a, h), _req(y1, y1.dtype), _req(y2, y1.dtype)
+    _call("dli_residual_add2", 1, _p(x), _p(y1), _p(y2), _p(a), _p(h), x.shape[0], x.shape[1], _dt(y1), _stream())
+    return x
+
+
+def concat_cast(a, b, out):
+    """out [rows, 2d] = [a | b] (a, b float32) in out's element type."""
+    _f32(a, b), _req(out, out.dtype)
+    _call("dli_concat_cast", 1, _p(a), _p(b), _p(out), a.shape[0], a.shape[1], _dt(out), _stream())
+    return out
+
+
+def rows_bias_f32(y, bias, x):
+    """x = y + bias (x, bias float32)."""
+    _req(y, y.dtype), _f32(bias, x)
+    _call("dli_rows_bias_f32", 1, _p(y), _p(bias), _p(x), x.shape[0], x.shape[1], _dt(y), _stream())
+    return x
 
 
 def scalar_rmsnorm(x, g: float, eps: float, out):
@@ -536,12 +567,14 @@ def attn_prep_append(proj, qbuf, k_cache, v_cache, row_ent, ent, page_table, H, 
 
 
 def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, G, D, V, scale, chunk=0, window=0,
-                sink=None, g_off=-1, cos_v=None, sin_v=None):
-    """Chunk- / window-masked attention with an optional sink and output gate over the paged cache -> out [rows, H*V]."""
+                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0):
+    """Chunk- / window-masked attention with an optional sink and output gate over the paged cache -> out [rows, H*V].
+    ldv: elements between value rows (0 = V); v_cache may be k_cache itself (values = leading part of the keys)."""
     _f32(qbuf, sink, cos_v, sin_v), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
     _call("dli_attn_ragged", 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(row_ent), _p(ent),
           _p(page_table), page_table.shape[1], k_cache.shape[2], qbuf.shape[0], H, G, D, V, float(scale), int(chunk),
-          int(window), _p(sink), proj.shape[1], g_off, _p(cos_v), _p(sin_v), _dt(k_cache), _stream())
+          int(window), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), int(ldv),
+          _dt(k_cache), _stream())
     return out
 
 
@@ -599,3 +632,74 @@ def postnorm_add_norm_conv_single(y, x, tail, w, ent, out, g_post: float, g_next
     _call("dli_postnorm_add_norm_conv_single", 1, _p(y), _p(x), _p(tail), _p(w), _p(ent), _p(out), x.shape[0], x.shape[1],
           w.shape[1], float(eps), float(g_post), float(g_next), _dt(out), _stream())
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Latent attention, state-space mixer, mixture of experts (latent_attn.cu, mamba2.cu, moe.cu)
+def latent_prep(proj, cq, pool, row_ent, ent, page_table, Q, K, R, q_off, kv_off, q_norm, kv_norm, eps, cos_t, sin_t):
+    """Query latent (normed) -> cq [rows, Q]; key/value latent (normed) and the rotated shared key part -> the pool
+    [pages, 1, page_size, K + R]."""
+    _req(proj, proj.dtype), _req(cq, proj.dtype), _req(pool, proj.dtype)
+    _f32(q_norm, kv_norm, cos_t, sin_t), _i32(row_ent, ent, page_table)
+    _call("dli_latent_prep", 1, _p(proj), _p(cq), _p(pool), _p(row_ent), _p(ent), _p(page_table), page_table.shape[1],
+          pool.shape[2], proj.shape[0], Q, K, R, proj.shape[1], q_off, kv_off, _p(q_norm), _p(kv_norm), float(eps),
+          _p(cos_t), _p(sin_t), cos_t.shape[0] if cos_t is not None else 0, _dt(proj), _stream())
+
+
+def latent_q_absorb(q, uk, qbuf, row_ent, ent, cos_t, sin_t, H, D, R, K):
+    """q [rows, H*(D+R)], uk [H*D, K] -> qbuf float32 [rows, H*(K+R)] = per head [uk[h]^T q_n | rot(q_r)]."""
+    _req(q, q.dtype), _req(uk, q.dtype), _f32(qbuf, cos_t, sin_t), _i32(row_ent, ent)
+    _call("dli_latent_q_absorb", 1, _p(q), _p(uk), _p(qbuf), _p(row_ent), _p(ent), _p(cos_t), _p(sin_t), q.shape[0], H, D,
+          R, K, _dt(q), _stream())
+    return qbuf
+
+
+def latent_v_up(o, uv, proj, out, H, V, K, g_off=-1):
+    """o [rows, H*K], uv [H*V, K] -> out [rows, H*V] = (uv[h] o[h]) * sigmoid(proj[:, g_off + h*V + v])."""
+    _req(o, o.dtype), _req(uv, o.dtype), _req(out, o.dtype), _req(proj, o.dtype)
+    _call("dli_latent_v_up", 1, _p(o), _p(uv), _p(proj), _p(out), o.shape[0], H, V, K,
+          proj.shape[1] if proj is not None else 0, g_off, _dt(o), _stream())
+    return out
+
+
+def conv1d_act_ragged(proj, tail, w, bias, row_ent, ent, out, off, act=1):
+    """Causal per-channel convolution (+ bias, SiLU) over columns [off, off + C) of proj -> out float32 [rows, C]; the
+    slots' histories tail float32 [slots, taps-1, C] are advanced."""
+    _req(proj, proj.dtype), _f32(tail, w, bias, out), _i32(row_ent, ent)
+    C, taps = w.shape
+    _call("dli_conv1d_act_ragged", 2 if taps > 1 else 1, _p(proj), _p(tail), _p(w), _p(bias), _p(row_ent), _p(ent), _p(out),
+          proj.shape[0], ent.numel() // 4, C, taps, proj.shape[1], off, int(act), _dt(proj), _stream())
+    return out
+
+
+def ssm_scan_ragged(xbc, proj, S, y, ent, H, V, N, G, dt_off, dt_bias, a_log, d_skip):
+    """The state-space recurrence over the rows of every entry; S float32 [slots, H, N, V] is advanced; y float32
+    [rows, H*V]."""
+    _f32(xbc, S, y, dt_bias, a_log, d_skip), _req(proj, proj.dtype), _i32(ent)
+    _call("dli_ssm_scan_ragged", 1, _p(xbc), _p(proj), _p(S), _p(y), _p(ent), ent.numel() // 4, H, V, N, G, proj.shape[1],
+          dt_off, _p(dt_bias), _p(a_log), _p(d_skip), _dt(proj), _stream())
+    return y
+
+
+def gated_group_rmsnorm(y, proj, w, out, groups, eps, z_off):
+    """out = groupnorm(y * silu(proj[:, z_off : z_off + d])) * w."""
+    _f32(y, w), _req(proj, proj.dtype), _req(out, proj.dtype)
+    _call("dli_gated_group_rmsnorm", 1, _p(y), _p(proj), _p(w), _p(out), y.shape[0], y.shape[1], int(groups), float(eps),
+          proj.shape[1], z_off, _dt(proj), _stream())
+    return out
+
+
+def moe_route(h, w_router, correction, wts, idw, sel_idx, sel_w, n_real, top):
+    """Router of a mixture of experts on float32 rows: dense weights wts [rows, n_real], pass-through weight idw [rows],
+    the choice sel_idx / sel_w [rows, top]."""
+    _f32(h, w_router, correction, wts, idw, sel_w), _i32(sel_idx)
+    _call("dli_moe_route", 1, _p(h), _p(w_router), _p(correction), _p(wts), _p(idw), _p(sel_idx), _p(sel_w), h.shape[0],
+          h.shape[1], w_router.shape[0], int(n_real), int(top), _stream())
+
+
+def moe_act(gu, wts, act, n_exp, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702):
+    """Clamped gated activation of all experts' stacked gate/up rows, times the routing weights."""
+    _req(gu, gu.dtype), _req(act, gu.dtype), _f32(wts)
+    _call("dli_moe_act", 1, _p(gu), _p(wts), _p(act), gu.shape[0], int(n_exp), int(ff), float(limit), int(ff_s),
+          float(limit_s), float(alpha), gu.shape[1], _dt(gu), _stream())
+    return act

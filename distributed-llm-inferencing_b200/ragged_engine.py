@@ -33,7 +33,7 @@ BF = torch.bfloat16
 
 @dataclass
 class MixerSpec:
-    kind: str                      # "attention" or "mlstm"
+    kind: str                      # "attention", "mlstm", "latent_attention" or "mamba2"
     heads: int
     kv_heads: int
     dim: int                       # query / key size per head
@@ -51,13 +51,46 @@ class MixerSpec:
     head_gate: bool = False        # sigmoid gate per head on the output
     # mlstm
     gate_cap: float = 0.0
+    # latent attention: queries and keys/values pass through low-rank latents; `dim` is the unrotated and `rot_dims`
+    # the rotated query/key size per head; the cache holds kv_rank + rot_dims numbers per position
+    kv_rank: int = 0
+    q_rank: int = 0
+    out_gate: bool = False         # sigmoid gate per output channel (head_gate: one per head)
+    # mamba2: state rows per head, B/C groups, groups of the gated output norm, taps of the x/B/C convolution
+    state: int = 0
+    groups: int = 1
+    norm_groups: int = 1
+    conv_taps: int = 0
+
+
+@dataclass
+class MoESpec:
+    """Mixture-of-experts feed-forward: `experts` gated experts of size ff, then `identity` router outputs that pass
+    the input through; `top` are used per token; a shared expert (shared_ff > 0) runs for every token."""
+    experts: int
+    identity: int
+    top: int
+    ff: int
+    limit: float                   # gate is cut at +limit, up at +-limit
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+    alpha: float = 1.702           # g * sigmoid(alpha * g)
+
+    @property
+    def total_ff(self) -> int:
+        return self.experts * self.ff + self.shared_ff
 
 
 @dataclass
 class LayerSpec:
     mixer: MixerSpec
-    ff: int = 0                    # feed-forward size, 0 = no feed-forward sublayer
+    ff: int = 0                    # dense feed-forward size, 0 = none
     weights_of: Optional[int] = None
+    moe: Optional[MoESpec] = None  # mixture-of-experts feed-forward
+    parallel: bool = False         # True: ONE grouped norm; mixer (through the input convolution) and feed-forward both
+                                   # read it and x += mixer + feed-forward.  False: pre-/post-normed sublayers in sequence
+    ckpt: Optional[int] = None     # the checkpoint's layer number when it differs from the position in `layers`
+    reenter: Optional[int] = None  # t: before this layer x <- W_loop [x | embedding output] + step[t]
 
 
 @dataclass
@@ -68,6 +101,9 @@ class HybridSpec:
     eps: float
     taps: int                      # taps of the input convolutions (1: the current input only, no state)
     layers: List[LayerSpec] = field(default_factory=list)
+    embed_scale: float = 1.0
+    norm_groups: int = 0           # > 0: the final norm (and the norm of parallel layers) is grouped with a weight vector
+    loop_passes: int = 0           # > 0: the model has the loop re-entry projection and per-pass vectors
 
     @property
     def n_layers(self) -> int:
@@ -115,9 +151,10 @@ class RaggedEngine:
         torch.cuda.set_device(self.device)
         self.max_batch, self.max_seq_len = int(max_batch), int(max_seq_len)
         self.is_first = self.is_last = self.has_head = True
-        self.attn_layers = [i for i, L in enumerate(spec.layers) if L.mixer.kind == "attention"]
-        shapes = [(spec.layers[i].mixer.kv_heads, spec.layers[i].mixer.dim, spec.layers[i].mixer.vdim)
-                  for i in self.attn_layers]
+        self.attn_layers = [i for i, L in enumerate(spec.layers) if L.mixer.kind in ("attention", "latent_attention")]
+        # latent attention caches ONE row [latent | rotated key part] per position and no values of its own
+        shapes = [(1, m.kv_rank + m.rot_dims, 0) if m.kind == "latent_attention" else (m.kv_heads, m.dim, m.vdim)
+                  for m in (spec.layers[i].mixer for i in self.attn_layers)]
         self.kv = PagedKVCache(len(shapes), 0, 0, page_size, self.max_batch, self.max_seq_len, self.device,
                                pool_tokens=kv_pool_tokens, layer_shapes=shapes, dtype=dtype)
         self.kv_index = {li: n for n, li in enumerate(self.attn_layers)}
@@ -132,6 +169,11 @@ class RaggedEngine:
                 self.slots.add(("S", i), m.heads, m.dim, m.vdim)
                 self.slots.add(("n", i), m.heads, m.dim)
                 self.slots.add(("m", i), m.heads)
+            if L.mixer.kind == "mamba2":
+                m = L.mixer
+                self.slots.add(("S", i), m.heads, m.state, m.vdim)
+                if m.conv_taps > 1:
+                    self.slots.add(("ctail", i), m.conv_taps - 1, m.heads * m.vdim + 2 * m.groups * m.state)
         self.lengths: Dict[int, int] = {}          # slot -> tokens the sequence holds
         self.w: Dict[str, object] = {}
         self.layers: Dict[int, dict] = {}
@@ -160,8 +202,8 @@ class RaggedEngine:
         return self._tables[key]
 
     def load_tensors(self, t: dict) -> None:
-        """t: {"embed", "head", "final_norm", "layers": {i: {...}}} with the layer tensors named as in
-        sokevik.layer_tensors (any dtype / device); linear weights [out, in]."""
+        """t: {"embed", "head", "final_norm", "layers": {i: {...}}} (+ "loop_in", "loop_step") with the layer tensors
+        named as in sokevik.layer_tensors / togalorn.layer_tensors (any dtype / device); linear weights [out, in]."""
         dev, E = self.device, self.dtype
         s = self.spec
 
@@ -170,19 +212,28 @@ class RaggedEngine:
             w = torch.cat([x.reshape(-1, x.shape[-1]) for x in ws], dim=0).to(E)
             pad = _ceil(w.shape[0], 16) - w.shape[0] if pad_rows else 0
             if pad:
-                w = torch.cat((w, torch.zeros(pad, w.shape[1], dtype=E)), dim=0)
+                w = torch.cat((w, torch.zeros(pad, w.shape[1], dtype=E, device=w.device)), dim=0)
             return w.contiguous().to(dev)
 
         def vec(x):
             return x.to(torch.float32).reshape(-1).contiguous().to(dev)
 
+        def f32(x):
+            return x.to(torch.float32).contiguous().to(dev)
+
         self.w = {"embed": t["embed"].to(E).contiguous().to(dev), "head": mat(t["head"]),
-                  "final_norm": float(t["final_norm"])}
+                  "final_norm": vec(t["final_norm"]) if s.norm_groups else float(t["final_norm"])}
+        if s.loop_passes:
+            self.w["loop_in"] = mat(t["loop_in"], pad_rows=False)
+            self.w["loop_step"] = f32(t["loop_step"])
         self.layers = {}
         for i, src in t["layers"].items():
             L, m = s.layers[i], s.layers[i].mixer
-            d = {"norm1": float(src["norm1"]), "norm1b": float(src["norm1b"])}
-            d["canon1"] = src["canon1"].to(torch.float32).contiguous().to(dev)
+            d = {"canon1": f32(src["canon1"])}
+            if L.parallel:
+                d["norm1"] = vec(src["norm1"])
+            else:
+                d["norm1"], d["norm1b"] = float(src["norm1"]), float(src["norm1b"])
             qn, kn, vn = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
             if m.kind == "attention":
                 d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"]) if m.head_gate else mat(src["q"], src["k"], src["v"])
@@ -190,16 +241,32 @@ class RaggedEngine:
                 d["q_norm"] = vec(src["q_norm"]) if m.qk_norm else None
                 d["k_norm"] = vec(src["k_norm"]) if m.qk_norm else None
                 d["sink"] = vec(src["sink"]) if m.sink else None
-            else:
+            elif m.kind == "mlstm":
                 gn = m.heads * m.vdim
                 d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"], src["i"], src["f"])
                 d["off"] = {"q": 0, "k": qn, "v": 2 * qn, "g": 2 * qn + gn, "i": 2 * qn + 2 * gn,
                             "f": 2 * qn + 2 * gn + m.heads}
                 d["i_b"], d["f_b"], d["out_norm"] = vec(src["i_b"]), vec(src["f_b"]), vec(src["out_norm"])
+            elif m.kind == "latent_attention":
+                # one projection of the mixer's input: query latent | key/value latent and rotated key part | output gate
+                d["w_proj"] = mat(src["dq"], src["dkv"], src["g"]) if m.out_gate else mat(src["dq"], src["dkv"])
+                d["off"] = {"cq": 0, "kv": m.q_rank, "g": m.q_rank + m.kv_rank + m.rot_dims if m.out_gate else -1}
+                d["w_uq"] = mat(src["uq"], pad_rows=False)
+                d["uk"], d["uv"] = mat(src["uk"], pad_rows=False), mat(src["uv"], pad_rows=False)
+                d["q_norm"], d["kv_norm"] = vec(src["dq_norm"]), vec(src["dkv_norm"])
+            elif m.kind == "mamba2":
+                inner, gn = m.heads * m.vdim, m.groups * m.state
+                d["w_proj"] = mat(src["in"])
+                d["off"] = {"z": 0, "x": inner, "dt": 2 * inner + 2 * gn}
+                d["conv_w"], d["conv_b"] = f32(src["conv"]), vec(src["conv_b"])
+                d["dt_bias"], d["a_log"], d["d_skip"] = vec(src["dt_bias"]), vec(src["A_log"]), vec(src["D"])
+                d["out_norm"] = vec(src["out_norm"])
+            else:
+                raise ValueError(f"layer {i}: mixer kind {m.kind!r}")
             d["wo"] = mat(src["o"], pad_rows=False)
             if L.ff:
                 d["norm2"], d["norm2b"] = float(src["norm2"]), float(src["norm2b"])
-                d["canon2"] = src["canon2"].to(torch.float32).contiguous().to(dev)
+                d["canon2"] = f32(src["canon2"])
                 # the tensor-core path interleaves gate and up rows so that silu(gate) * up is the GEMM's epilogue
                 d["packed"] = E == BF and L.ff % 128 == 0 and s.width % 8 == 0
                 if d["packed"]:
@@ -207,6 +274,18 @@ class RaggedEngine:
                 else:
                     d["w_gu"] = torch.cat((src["gate"], src["up"]), dim=0).to(E).contiguous().to(dev)
                 d["w_down"] = mat(src["down"], pad_rows=False)
+            if L.moe is not None:
+                # all experts as ONE gate/up matrix (per expert [gate; up], the shared expert last) and ONE down matrix
+                # over the concatenated expert activations: the routing weights are applied between the two
+                e = L.moe
+                blocks = [x for g_, u_, _ in src["experts"] for x in (g_, u_)]
+                downs = [d_ for _, _, d_ in src["experts"]]
+                if e.shared_ff:
+                    blocks += [src["shared"][0], src["shared"][1]]
+                    downs.append(src["shared"][2])
+                d["w_gu"] = mat(*blocks)
+                d["w_down"] = torch.cat([x.to(E) for x in downs], dim=1).contiguous().to(dev)
+                d["w_router"], d["corr"] = f32(src["router"]), vec(src["correction"])
             self.layers[i] = d
 
     def weight_bytes(self) -> int:
@@ -249,8 +328,10 @@ class RaggedEngine:
         mx = [L.mixer for L in s.layers]
         n_proj = max(d["w_proj"].shape[0] for d in self.layers.values())
         n_mix = max(m.heads * m.vdim for m in mx)
-        n_q = max([m.heads * m.dim for m in mx if m.kind == "attention"] or [1])
-        ff = max([L.ff for L in s.layers] or [0])
+        n_q = max([m.heads * m.dim for m in mx if m.kind == "attention"] +
+                  [m.heads * (m.kv_rank + m.rot_dims) for m in mx if m.kind == "latent_attention"] + [1])
+        ff = max([L.moe.total_ff if L.moe is not None else L.ff for L in s.layers] or [0])
+        n_gu = max([d["w_gu"].shape[0] for d in self.layers.values() if "w_gu" in d] or [1])
         f32 = torch.float32
         self._x = torch.empty(rows, s.width, dtype=f32, device=dev)
         self._hn = torch.empty(rows, s.width, dtype=f32, device=dev)
@@ -261,7 +342,27 @@ class RaggedEngine:
         self._oscr = torch.empty(rows * n_mix, dtype=f32, device=dev)
         self._y = torch.empty(rows, s.width, dtype=E, device=dev)
         self._act = torch.empty(rows * max(ff, 1), dtype=E, device=dev)
-        self._gu = torch.empty(rows * max(2 * ff, 1), dtype=E, device=dev)
+        self._gu = torch.empty(rows * max(2 * ff, n_gu, 1), dtype=E, device=dev)
+        lat = [m for m in mx if m.kind == "latent_attention"]
+        if lat:
+            self._cq = torch.empty(rows * max(m.q_rank for m in lat), dtype=E, device=dev)
+            self._q = torch.empty(rows * max(m.heads * (m.dim + m.rot_dims) for m in lat), dtype=E, device=dev)
+            self._olat = torch.empty(rows * max(m.heads * m.kv_rank for m in lat), dtype=E, device=dev)
+        ssm = [m for m in mx if m.kind == "mamba2"]
+        if ssm:
+            self._xbc = torch.empty(rows * max(m.heads * m.vdim + 2 * m.groups * m.state for m in ssm), dtype=f32, device=dev)
+        if any(L.parallel for L in s.layers):
+            self._he = torch.empty(rows, s.width, dtype=E, device=dev)
+            self._y2 = torch.empty(rows, s.width, dtype=E, device=dev)
+        moes = [L.moe for L in s.layers if L.moe is not None]
+        if moes:
+            self._wts = torch.empty(rows * max(e.experts for e in moes), dtype=f32, device=dev)
+            self._idw = torch.empty(rows, dtype=f32, device=dev)
+            self._sel_idx = torch.empty(rows * max(e.top for e in moes), dtype=torch.int32, device=dev)
+            self._sel_w = torch.empty(rows * max(e.top for e in moes), dtype=f32, device=dev)
+        if s.loop_passes:
+            self._x0 = torch.empty(rows, s.width, dtype=f32, device=dev)
+            self._cat = torch.empty(rows, 2 * s.width, dtype=E, device=dev)
         self._hw = torch.empty(max(self.max_batch, 8), s.width, dtype=E, device=dev)
         self._ws_rows = rows
         self._graphs.clear()  # captured graphs hold the old workspace pointers
@@ -280,8 +381,9 @@ class RaggedEngine:
     def _splitk(self) -> torch.Tensor:
         """Zero-filled scratch of the split-K projections (self-resetting; calls are ordered on one stream)."""
         if getattr(self, "_sk", None) is None:
-            n_max = max([self.w["head"].shape[0]] + [max(d["w_proj"].shape[0], d["w_gu"].shape[0] if "w_gu" in d else 0,
-                                                         self.spec.width) for d in self.layers.values()])
+            n_max = max([self.w["head"].shape[0], self.spec.width] +
+                        [v.shape[0] for d in self.layers.values() for k, v in d.items() if k.startswith("w") and
+                         isinstance(v, torch.Tensor) and v.dim() == 2])
             self._sk = torch.zeros(ops.gemm_splitk_scratch_bytes(128, n_max), dtype=torch.uint8, device=self.device)
         return self._sk
 
@@ -413,11 +515,27 @@ class RaggedEngine:
                 ops.postnorm_add_norm(y_prev, x, g_post, s.eps, hn, g_next)
             ops.causal_conv_ragged(hn, tail, taps_w, d_rent, d_ent, hc)  # one tap: no tail, h * (1 + w)
 
-        ops.embedding_f32(d_tok, self.w["embed"], x)
+        x0 = self._x0[:rows] if s.loop_passes else None
+        ops.embedding_f32(d_tok, self.w["embed"], x, s.embed_scale, out2=x0)
         pt = self.kv.page_table
         y_prev, g_prev = None, 1.0
         for li, L in enumerate(s.layers):
             P, m = self.layers[s.source(li)], L.mixer
+            if L.reenter is not None or L.parallel:
+                if y_prev is not None:  # close the sequential sublayer before it
+                    ops.postnorm_add_norm(y_prev, x, g_prev, s.eps)
+                    y_prev = None
+            if L.reenter is not None:
+                # a pass of the loop starts from a projection of [x | embedding output] plus the pass's vector
+                cat = self._cat[:rows]
+                ops.concat_cast(x, x0, cat)
+                self._lin(cat, self.w["loop_in"], y)
+                ops.rows_bias_f32(y, self.w["loop_step"][L.reenter], x)
+            if L.parallel:
+                self._parallel_layer(li, L, P, rows, n_ent, views, long_step, tiles)
+                if self.layer_trace is not None:
+                    self.layer_trace.append(x.clone())
+                continue
             enter_sublayer(y_prev, g_prev, P["norm1"], self.slots.tensors.get(("tail1", li)), P.get("canon1"))
             n_proj = P["w_proj"].shape[0]
             proj = self._proj[:rows * n_proj].view(rows, n_proj)
@@ -478,7 +596,12 @@ class RaggedEngine:
                 ops.postnorm_add_norm(y, x, g_post, s.eps)
                 self.layer_trace.append(x.clone())
                 y_prev = None
-        if y_prev is None:
+        if s.norm_groups:
+            if y_prev is not None:
+                ops.postnorm_add_norm(y_prev, x, g_prev, s.eps)
+            if nw:
+                ops.group_rmsnorm(x, self.w["final_norm"], s.norm_groups, s.eps, hn=hn)
+        elif y_prev is None:
             ops.scalar_rmsnorm(x, self.w["final_norm"], s.eps, hn)
         else:
             ops.postnorm_add_norm(y_prev, x, g_prev, s.eps, hn, self.w["final_norm"])
@@ -490,6 +613,78 @@ class RaggedEngine:
         logits = logits_out[:nw] if logits_out is not None else torch.empty(nw, vp, dtype=E, device=dev)
         self._lin(hw, self.w["head"], logits)
         return logits
+
+    # ------------------------------------------------------------------ layers with side-by-side sublayers
+    def _parallel_layer(self, li, L, P, rows, n_ent, views, long_step, tiles):
+        """h = groupnorm(x); x += mixer(h + conv(h)) + feed-forward(h)."""
+        s, E = self.spec, self.dtype
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        x, hn, hc, he, y = self._x[:rows], self._hn[:rows], self._hc[:rows], self._he[:rows], self._y[:rows]
+        has_ff = L.moe is not None
+        ops.group_rmsnorm(x, P["norm1"], s.norm_groups, s.eps, hn=hn, he=he if has_ff else None)
+        ops.causal_conv_ragged(hn, self.slots.tensors.get(("tail1", li)), P["canon1"], d_rent, d_ent, hc)
+        m = L.mixer
+        n_proj = P["w_proj"].shape[0]
+        proj = self._proj[:rows * n_proj].view(rows, n_proj)
+        self._lin(hc, P["w_proj"], proj)
+        n_mix = m.heads * m.vdim
+        mix = self._mix[:rows * n_mix].view(rows, n_mix)
+        if m.kind == "latent_attention":
+            self._latent_attention(li, m, P, proj, mix, rows, views)
+        elif m.kind == "mamba2":
+            self._mamba2(li, m, P, proj, mix, rows, views)
+        else:
+            raise ValueError(f"layer {li}: mixer {m.kind!r} has no side-by-side form")
+        self._lin(mix, P["wo"], y)
+        if not has_ff:
+            ops.residual_add2(x, y)
+            return
+        e = L.moe
+        y2 = self._y2[:rows]
+        wts = self._wts[:rows * e.experts].view(rows, e.experts)
+        idw = self._idw[:rows]
+        ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, self._sel_idx[:rows * e.top].view(rows, e.top),
+                      self._sel_w[:rows * e.top].view(rows, e.top), e.experts, e.top)
+        n_gu = P["w_gu"].shape[0]
+        gu = self._gu[:rows * n_gu].view(rows, n_gu)
+        self._lin(he, P["w_gu"], gu)
+        act = self._act[:rows * e.total_ff].view(rows, e.total_ff)
+        ops.moe_act(gu, wts, act, e.experts, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha)
+        self._lin(act, P["w_down"], y2)
+        ops.residual_add2(x, y, y2, idw if e.identity else None, hn if e.identity else None)
+
+    def _latent_attention(self, li, m, P, proj, mix, rows, views):
+        """Attention over the cached latents: the heads' key up-projections are folded into the queries, the value
+        up-projections applied to the attention output (one shared key/value row per position)."""
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        pool = self.kv.k[self.kv_index[li]]
+        K, R, H = m.kv_rank, m.rot_dims, m.heads
+        cos_t, sin_t = self._table(m.rot_base, R, None) if R else (None, None)
+        cq = self._cq[:rows * m.q_rank].view(rows, m.q_rank)
+        off = P["off"]
+        ops.latent_prep(proj, cq, pool, d_rent, d_ent, self.kv.page_table, m.q_rank, K, R, off["cq"], off["kv"],
+                        P["q_norm"], P["kv_norm"], self.spec.eps, cos_t, sin_t)
+        q = self._q[:rows * H * (m.dim + R)].view(rows, H * (m.dim + R))
+        self._lin(cq, P["w_uq"], q)
+        qbuf = self._qbuf[:rows * H * (K + R)].view(rows, H * (K + R))
+        ops.latent_q_absorb(q, P["uk"], qbuf, d_rent, d_ent, cos_t, sin_t, H, m.dim, R, K)
+        olat = self._olat[:rows * H * K].view(rows, H * K)
+        ops.attn_ragged(qbuf, pool, pool, None, olat, d_rent, d_ent, self.kv.page_table, H, 1, K + R, K, m.scale,
+                        ldv=K + R)
+        ops.latent_v_up(olat, P["uv"], proj if m.out_gate else None, mix, H, m.vdim, K, g_off=off["g"])
+
+    def _mamba2(self, li, m, P, proj, mix, rows, views):
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        inner, gn = m.heads * m.vdim, m.groups * m.state
+        C = inner + 2 * gn
+        off = P["off"]
+        xbc = self._xbc[:rows * C].view(rows, C)
+        ops.conv1d_act_ragged(proj, self.slots.tensors.get(("ctail", li)), P["conv_w"], P["conv_b"], d_rent, d_ent, xbc,
+                              off["x"], act=1)
+        yss = self._oscr[:rows * inner].view(rows, inner)
+        ops.ssm_scan_ragged(xbc, proj, self.slots[("S", li)], yss, d_ent, m.heads, m.vdim, m.state, m.groups, off["dt"],
+                            P["dt_bias"], P["a_log"], P["d_skip"])
+        ops.gated_group_rmsnorm(yss, proj, P["out_norm"], mix, m.norm_groups, self.spec.eps, off["z"])
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()

@@ -401,8 +401,20 @@ int dli_decode_advance(const int32_t* tokens, int32_t* token_log, int32_t* posit
  * caches: 0 = bf16, 1 = float (true fp32 arithmetic).  The residual stream x,
  * every norm, convolution state, recurrent state, angle, score and softmax weight
  * is fp32 for both. */
-int dli_embedding_f32(const int32_t* ids, const void* table, float* x, int rows, int d, int vocab, int dt,
+/* x = table[ids] * scale as fp32; x2 (optional) receives the same rows (a model that re-reads its embedding output). */
+int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, int rows, int d, int vocab, float scale,
+                      int dt, dli_stream_t stream);
+/* RMS norm in `groups` equal consecutive parts of the row, each by its own root mean square, times w [d] fp32;
+ * hn (fp32) and he (element type dt) are optional outputs. */
+int dli_group_rmsnorm(const float* x, const float* w, float* hn, void* he, int rows, int d, int groups, float eps, int dt,
                       dli_stream_t stream);
+/* x += y1 + y2 + a[row] * h (y2, and a with h, optional): residual add of sublayers that run side by side. */
+int dli_residual_add2(float* x, const void* y1, const void* y2, const float* a, const float* h, int rows, int d, int dt,
+                      dli_stream_t stream);
+/* out [rows, 2d] = [a | b] in the element type. */
+int dli_concat_cast(const float* a, const float* b, void* out, int rows, int d, int dt, dli_stream_t stream);
+/* x = y + bias (bias [d] fp32 or NULL). */
+int dli_rows_bias_f32(const void* y, const float* bias, float* x, int rows, int d, int dt, dli_stream_t stream);
 /* hn = x / sqrt(mean(x^2) + eps) * g, one weight g per norm. */
 int dli_scalar_rmsnorm_f32(const float* x, float* hn, int rows, int d, float eps, float g, dli_stream_t stream);
 /* x += y / rms(y) * g_post; hn = x / rms(x) * g_next (hn may be NULL). */
@@ -430,7 +442,8 @@ int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_st
  * [pages, G, page_size, D] / [pages, G, page_size, V].  dli_attn_ragged: scores (q . k) * scale over the keys the
  * chunk mask (chunk > 0: same block of `chunk` positions) and the window (window > 0) leave, softmax with an optional
  * sink term exp(sink[h]) in the denominator, output turned back by the row's position (cos_v / sin_v) and multiplied
- * by sigmoid(proj[row, g_off + h]) (g_off < 0: no gate) -> out [rows, H, V]. */
+ * by sigmoid(proj[row, g_off + h]) (g_off < 0: no gate) -> out [rows, H, V].  ldv: elements between the value rows of
+ * consecutive positions (0 = V); with v_cache == k_cache and ldv = D the values are the first V entries of the keys. */
 int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_cache, const int32_t* row_ent,
                          const int32_t* ent, const int32_t* page_table, int max_pages, int page_size, int rows, int H,
                          int G, int D, int V, int rd, int ldp, int q_off, int k_off, int v_off, const float* q_norm,
@@ -439,7 +452,7 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
-                    int g_off, const float* cos_v, const float* sin_v, int dt, dli_stream_t stream);
+                    int g_off, const float* cos_v, const float* sin_v, int ldv, int dt, dli_stream_t stream);
 
 /* The same attention for steps that hold portions of prompts, on the tensor cores (bf16 caches only): one CTA per
  * 64-row query tile of an entry and query head; tiles[2t] = entry, tiles[2t+1] = first row of the tile within the
@@ -469,6 +482,48 @@ int dli_mlstm_ragged_parallel(const void* proj, float* o_scratch, void* y, const
                               int q_off, int k_off, int v_off, int i_off, int f_off, int g_off, const float* i_bias,
                               const float* f_bias, float cap, const float* out_w, float eps, float* S, float* n, float* m,
                               int dt, dli_stream_t stream);
+
+/* Latent attention: per position only the normed key/value latent c [K] and one rotated key part k_r [R] are cached,
+ * as rows [c | k_r] of a pool [pages, 1, page_size, K + R].  dli_latent_prep: c_q = rmsnorm(proj[q_off : +Q]) * q_norm
+ * -> cq [rows, Q]; c = rmsnorm(proj[kv_off : +K]) * kv_norm and k_r = rot(proj[kv_off + K : +R]) -> the pool.
+ * dli_latent_q_absorb: q [rows, H, D + R] and uk [H*D, K] -> qbuf [rows, H, K + R] fp32 = [uk[h]^T q_n | rot(q_r)], so
+ * that dli_attn_ragged over the pool (G = 1, key size K + R, value size K, ldv = K + R) gives each head's output in
+ * the latent; dli_latent_v_up: out [rows, H*V] = (uv[h] o[row, h]) * sigmoid(proj[row, g_off + h*V + v]). */
+int dli_latent_prep(const void* proj, void* cq, void* pool, const int32_t* row_ent, const int32_t* ent,
+                    const int32_t* page_table, int max_pages, int page_size, int rows, int Q, int K, int R, int ldp,
+                    int q_off, int kv_off, const float* q_norm, const float* kv_norm, float eps, const float* cos_t,
+                    const float* sin_t, int table_len, int dt, dli_stream_t stream);
+int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_t* row_ent, const int32_t* ent,
+                        const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int dt,
+                        dli_stream_t stream);
+int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, int rows, int H, int V, int K, int ldp,
+                    int g_off, int dt, dli_stream_t stream);
+
+/* Selective state-space mixer (Mamba-2 form).  dli_conv1d_act_ragged: causal per-channel convolution (w [C, taps]
+ * fp32, tap taps-1 is the current row; bias [C] or NULL; act 1 = SiLU) over columns [off, off + C) of proj, history
+ * in tail [slots, taps-1, C] fp32 (advanced) -> out [rows, C] fp32.  dli_ssm_scan_ragged: xbc [rows, H*V + 2*G*N] fp32
+ * = x | B | C, dt = softplus(proj[row, dt_off + h] + dt_bias[h]), S [slots, H, N, V] fp32 is read and advanced:
+ * S = exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + d_skip[h] x -> y [rows, H*V] fp32.
+ * dli_gated_group_rmsnorm: out = groupnorm(y * silu(proj[row, z_off : +d])) * w. */
+int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const float* bias, const int32_t* row_ent,
+                          const int32_t* ent, float* out, int rows, int n_ent, int C, int taps, int ldp, int off, int act,
+                          int dt, dli_stream_t stream);
+int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, const int32_t* ent, int n_ent, int H, int V,
+                        int N, int G, int ldp, int dt_off, const float* dt_bias, const float* a_log, const float* d_skip,
+                        int dt, dli_stream_t stream);
+int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, void* out, int rows, int d, int groups,
+                            float eps, int ldp, int z_off, int dt, dli_stream_t stream);
+
+/* Mixture of experts.  dli_moe_route: h [rows, d] fp32, w_router [n_out, d] fp32, correction [n_out] or NULL; softmax
+ * over all n_out, the `top` largest of score + correction are chosen, weights = their scores / (their sum + 1e-20);
+ * outputs n_real.. are experts that return their input.  wts [rows, n_real] dense (0 = not chosen), idw [rows] summed
+ * weight of the chosen pass-through experts, sel_idx / sel_w [rows, top] the choice.  dli_moe_act: gu [rows, ld] =
+ * per routed expert [gate ff | up ff], then the shared expert's [gate ff_s | up ff_s]; act [rows, n_exp*ff + ff_s] =
+ * min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1) * weight (shared: weight 1). */
+int dli_moe_route(const float* h, const float* w_router, const float* correction, float* wts, float* idw, int32_t* sel_idx,
+                  float* sel_w, int rows, int d, int n_out, int n_real, int top, dli_stream_t stream);
+int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp, int ff, float limit, int ff_s,
+                float limit_s, float alpha, int ld, int dt, dli_stream_t stream);
 
 #ifdef __cplusplus
 }
