@@ -170,3 +170,11 @@ def forward(cfg: dict, sd: Dict[str, torch.Tensor], tokens: List[int]):
         trace.append(x.clone())
     hf = grouped_rms_norm(x, sd["final.norm"].to(F64), groups, eps)
     return hf @ sd["head"].to(F64).T, torch.stack(trace)
+
+
+def greedy(cfg: dict, sd: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    """The prompt followed by n_new tokens, each the argmax of the logits at the last position."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(forward(cfg, sd, toks)[0][-1].argmax()))
+    return toks
