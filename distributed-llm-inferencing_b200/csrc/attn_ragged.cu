@@ -297,8 +297,10 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
     const uint32_t dK = sK + stage * kKBytes, dV = sV + stage * kVBytes;
     const int tok = tile * kRtTile + lrow;
     const bool valid = tok <= p_last;
-    size_t rowbase = 0;
-    if (valid) rowbase = ((size_t)pt[tok / a.page_size] * a.G + g) * a.page_size + tok % a.page_size;
+    // rows past the last position copy nothing (size 0) but still name an address: that of the last valid row, so
+    // that a pool given as a window of pages is never addressed outside the window
+    const int tk = valid ? tok : p_last;
+    const size_t rowbase = ((size_t)pt[tk / a.page_size] * a.G + g) * a.page_size + tk % a.page_size;
     const bf16* ksrc = kc + rowbase * DK;
     const bf16* vsrc = vc + rowbase * DV;
 #pragma unroll

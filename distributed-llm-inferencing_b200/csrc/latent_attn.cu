@@ -102,6 +102,10 @@ latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float*
   __syncthreads();
   const E* w = uk + (size_t)h * D * K;
   for (int k = tid; k < K; k += blockDim.x) {
+    if (uk == nullptr) {  // no folding: K == D, the unrotated part passes through
+      for (int r = 0; r < nr; ++r) qbuf[((size_t)(r0 + r) * H + h) * (K + R) + k] = qs[r * D + k];
+      continue;
+    }
     float acc[kLatRows];
 #pragma unroll
     for (int r = 0; r < kLatRows; ++r) acc[r] = 0.f;
@@ -167,6 +171,43 @@ latent_v_up_kernel(const E* __restrict__ o, const E* __restrict__ uv, const E* _
   }
 }
 
+// For steps that hold portions of prompts: per-head keys [k_n | k_r] and values of every cached position of a page
+// range, from kv [n, H*D + H*V] (the up-projections of the cached latents) and the pool rows [n, K + R], into pools
+// of the layout the tensor-core attention reads: kx [pages, H, page_size, D + R], vx [pages, H, page_size, V].
+template <typename E>
+__global__ void __launch_bounds__(256)
+latent_expand_kernel(const E* __restrict__ kv, const E* __restrict__ pool, E* __restrict__ kx, E* __restrict__ vx, int H,
+                     int D, int R, int V, int K, int page_size) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t n = blockIdx.x;
+  const size_t page = n / page_size, off = n % page_size;
+  const E* kvr = kv + n * (size_t)(H * D + H * V);
+  const E* pr = pool + n * (size_t)(K + R) + K;
+  const int DK = D + R;
+  for (int i = threadIdx.x; i < H * DK; i += blockDim.x) {
+    const int h = i / DK, c = i - h * DK;
+    kx[((page * H + h) * page_size + off) * DK + c] = c < D ? kvr[h * D + c] : pr[c - D];
+  }
+  for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
+    const int h = i / V, c = i - h * V;
+    vx[((page * H + h) * page_size + off) * V + c] = kvr[H * D + i];
+  }
+}
+
+// out[row, c] *= sigmoid(proj[row, g_off + c])
+template <typename E>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(E* __restrict__ out, const E* __restrict__ proj, int n, int ldp, int g_off) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float g = 1.f / (1.f + expf(-l_to_f(proj[row * ldp + g_off + c])));
+    out[row * n + c] = l_from_f<E>(l_to_f(out[row * n + c]) * g);
+  }
+}
+
 }  // namespace dli
 
 using namespace dli;
@@ -193,7 +234,8 @@ int dli_latent_prep(const void* proj, void* cq, void* pool, const int32_t* row_e
 int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_t* row_ent, const int32_t* ent,
                         const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int dt,
                         dli_stream_t stream) {
-  DLI_CHECK_ARG(q && uk && qbuf && row_ent && ent, "dli_latent_q_absorb: null pointer");
+  DLI_CHECK_ARG(q && qbuf && row_ent && ent, "dli_latent_q_absorb: null pointer");
+  DLI_CHECK_ARG(uk || K == D, "dli_latent_q_absorb: without an up-projection the output size is the query size");
   DLI_CHECK_ARG(H > 0 && D > 0 && K > 0 && R >= 0 && R % 2 == 0 && (R == 0 || (cos_t && sin_t)) &&
                     (size_t)kLatRows * D * sizeof(float) <= 48 * 1024,
                 "dli_latent_q_absorb: H=%d D=%d R=%d K=%d", H, D, R, K);
@@ -220,6 +262,28 @@ int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, 
   const size_t smem = (size_t)kLatRows * K * sizeof(float);
   if (dt == 0) DLI_LAUNCH("latent_v_up", latent_v_up_kernel<bf16>, grid, dim3(256), smem, s, (const bf16*)o, (const bf16*)uv, (const bf16*)proj, (bf16*)out, rows, H, V, K, ldp, g_off);
   else DLI_LAUNCH("latent_v_up", latent_v_up_kernel<float>, grid, dim3(256), smem, s, (const float*)o, (const float*)uv, (const float*)proj, (float*)out, rows, H, V, K, ldp, g_off);
+  return DLI_OK;
+}
+
+int dli_latent_expand(const void* kv, const void* pool, void* kx, void* vx, int n, int H, int D, int R, int V, int K,
+                      int page_size, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(kv && pool && kx && vx && H > 0 && D > 0 && V > 0 && K > 0 && R >= 0 && page_size > 0 && n % page_size == 0,
+                "dli_latent_expand: null pointer or bad shape");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (n <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("latent_expand", latent_expand_kernel<bf16>, dim3(n), dim3(256), 0, s, (const bf16*)kv, (const bf16*)pool, (bf16*)kx, (bf16*)vx, H, D, R, V, K, page_size);
+  else DLI_LAUNCH("latent_expand", latent_expand_kernel<float>, dim3(n), dim3(256), 0, s, (const float*)kv, (const float*)pool, (float*)kx, (float*)vx, H, D, R, V, K, page_size);
+  return DLI_OK;
+}
+
+int dli_sigmoid_gate(void* out, const void* proj, int rows, int n, int ldp, int g_off, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(out && proj && n > 0 && g_off >= 0 && ldp >= g_off + n, "dli_sigmoid_gate: null pointer or bad shape");
+  DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("sigmoid_gate", sigmoid_gate_kernel<bf16>, dim3(rows), dim3(256), 0, s, (bf16*)out, (const bf16*)proj, n, ldp, g_off);
+  else DLI_LAUNCH("sigmoid_gate", sigmoid_gate_kernel<float>, dim3(rows), dim3(256), 0, s, (float*)out, (const float*)proj, n, ldp, g_off);
   return DLI_OK;
 }
 

@@ -583,13 +583,16 @@ def attn_ragged_tc_supported(D, V, dtype) -> bool:
 
 
 def attn_ragged_tc(qbuf, k_cache, v_cache, proj, out, ent, tiles, page_table, H, G, D, V, scale, chunk=0, window=0,
-                   sink=None, g_off=-1, cos_v=None, sin_v=None):
+                   sink=None, g_off=-1, cos_v=None, sin_v=None, page_base=0):
     """attn_ragged for steps with portions of prompts, on the tensor cores: tiles int32 [n_tiles, 2] = (entry, first
-    row of the 64-row query tile within the entry)."""
+    row of the 64-row query tile within the entry).  page_base: k_cache / v_cache hold pages page_base.. of the pool only
+    (the pages the step's sequences use must all lie in that range)."""
     _f32(qbuf, sink, cos_v, sin_v), _i32(ent, tiles, page_table), _req(out), _req(proj), _req(k_cache), _req(v_cache)
-    _call("dli_attn_ragged_tc", 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(ent), _p(tiles),
+    kb = page_base * k_cache.stride(0) * k_cache.element_size()
+    vb = page_base * v_cache.stride(0) * v_cache.element_size()
+    _call("dli_attn_ragged_tc", 1, _p(qbuf), _p(k_cache) - kb, _p(v_cache) - vb, _p(proj), _p(out), _p(ent), _p(tiles),
           tiles.numel() // 2, _p(page_table), page_table.shape[1], k_cache.shape[2], H, G, D, V, float(scale), int(chunk),
-          int(window), _p(sink), proj.shape[1], g_off, _p(cos_v), _p(sin_v), _stream())
+          int(window), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), _stream())
     return out
 
 
@@ -647,7 +650,8 @@ def latent_prep(proj, cq, pool, row_ent, ent, page_table, Q, K, R, q_off, kv_off
 
 
 def latent_q_absorb(q, uk, qbuf, row_ent, ent, cos_t, sin_t, H, D, R, K):
-    """q [rows, H*(D+R)], uk [H*D, K] -> qbuf float32 [rows, H*(K+R)] = per head [uk[h]^T q_n | rot(q_r)]."""
+    """q [rows, H*(D+R)], uk [H*D, K] -> qbuf float32 [rows, H*(K+R)] = per head [uk[h]^T q_n | rot(q_r)]; uk None
+    (K == D): [q_n | rot(q_r)]."""
     _req(q, q.dtype), _req(uk, q.dtype), _f32(qbuf, cos_t, sin_t), _i32(row_ent, ent)
     _call("dli_latent_q_absorb", 1, _p(q), _p(uk), _p(qbuf), _p(row_ent), _p(ent), _p(cos_t), _p(sin_t), q.shape[0], H, D,
           R, K, _dt(q), _stream())
@@ -659,6 +663,21 @@ def latent_v_up(o, uv, proj, out, H, V, K, g_off=-1):
     _req(o, o.dtype), _req(uv, o.dtype), _req(out, o.dtype), _req(proj, o.dtype)
     _call("dli_latent_v_up", 1, _p(o), _p(uv), _p(proj), _p(out), o.shape[0], H, V, K,
           proj.shape[1] if proj is not None else 0, g_off, _dt(o), _stream())
+    return out
+
+
+def latent_expand(kv, pool_rows, kx, vx, H, D, R, V, K, page_size):
+    """kv [n, H*D + H*V] (up-projections of n consecutive pool rows) and those rows [n, K+R] -> per-head key and
+    value pools kx [n/page_size, H, page_size, D+R], vx [n/page_size, H, page_size, V]."""
+    _req(kv, kv.dtype), _req(pool_rows, kv.dtype), _req(kx, kv.dtype), _req(vx, kv.dtype)
+    _call("dli_latent_expand", 1, _p(kv), _p(pool_rows), _p(kx), _p(vx), kv.shape[0], H, D, R, V, K, page_size, _dt(kv),
+          _stream())
+
+
+def sigmoid_gate(out, proj, g_off):
+    """out[row, c] *= sigmoid(proj[row, g_off + c])."""
+    _req(out, out.dtype), _req(proj, out.dtype)
+    _call("dli_sigmoid_gate", 1, _p(out), _p(proj), out.shape[0], out.shape[1], proj.shape[1], g_off, _dt(out), _stream())
     return out
 
 

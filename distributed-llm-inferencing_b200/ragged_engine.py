@@ -186,6 +186,7 @@ class RaggedEngine:
         self.pad_token_id: Optional[int] = None
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
         self.tc_min_rows = int(os.environ.get("DLI_RAGGED_TC_MIN_ROWS", "16"))  # portions from this size: tensor-core attention
+        self.latent_expand_max_elems = 1 << 31     # scratch bound (4 GiB in bf16) of the per-head expansion of cached latents
         self.mlstm_parallel_max_floats = 1 << 28   # scratch bound (1 GiB) of the block-parallel mLSTM; beyond it: blocks in order
         self.layer_trace: Optional[list] = None    # set to [] to collect the residual stream after every layer
         ops.set_pdl(os.environ.get("DLI_PDL", "1") == "1")
@@ -254,6 +255,12 @@ class RaggedEngine:
                 d["w_uq"] = mat(src["uq"], pad_rows=False)
                 d["uk"], d["uv"] = mat(src["uk"], pad_rows=False), mat(src["uv"], pad_rows=False)
                 d["q_norm"], d["kv_norm"] = vec(src["dq_norm"]), vec(src["dkv_norm"])
+                if E == BF and ops.attn_ragged_tc_supported(m.dim + m.rot_dims, m.vdim, E):
+                    # steps with portions of prompts expand the cached latents to per-head keys and values with ONE GEMM
+                    # over the pool rows [latent | rotated key part]: [uk; uv] with zero columns under the rotated part
+                    ukv = torch.cat((src["uk"], src["uv"]), dim=0).to(E)
+                    d["w_ukv"] = torch.cat((ukv, torch.zeros(ukv.shape[0], m.rot_dims, dtype=E, device=ukv.device)),
+                                           dim=1).contiguous().to(dev)
             elif m.kind == "mamba2":
                 inner, gn = m.heads * m.vdim, m.groups * m.state
                 d["w_proj"] = mat(src["in"])
@@ -329,7 +336,7 @@ class RaggedEngine:
         n_proj = max(d["w_proj"].shape[0] for d in self.layers.values())
         n_mix = max(m.heads * m.vdim for m in mx)
         n_q = max([m.heads * m.dim for m in mx if m.kind == "attention"] +
-                  [m.heads * (m.kv_rank + m.rot_dims) for m in mx if m.kind == "latent_attention"] + [1])
+                  [m.heads * (max(m.kv_rank, m.dim) + m.rot_dims) for m in mx if m.kind == "latent_attention"] + [1])
         ff = max([L.moe.total_ff if L.moe is not None else L.ff for L in s.layers] or [0])
         n_gu = max([d["w_gu"].shape[0] for d in self.layers.values() if "w_gu" in d] or [1])
         f32 = torch.float32
@@ -421,6 +428,11 @@ class RaggedEngine:
             tokens += [int(t) for t in toks]
         if grew:
             self.kv.commit()
+        self._step_pages = None
+        if self.attn_layers:
+            used = [p for slot, toks in batch
+                    for p in self.kv.owned[slot][:(self.lengths[slot] + len(toks) + self.kv.page_size - 1) // self.kv.page_size]]
+            self._step_pages = (min(used), max(used))
         # steps that hold a portion of a prompt run attention in 64-row query tiles on the tensor cores
         tiles: List[int] = []
         if any(len(t) >= self.tc_min_rows for _, t in batch):
@@ -630,7 +642,7 @@ class RaggedEngine:
         n_mix = m.heads * m.vdim
         mix = self._mix[:rows * n_mix].view(rows, n_mix)
         if m.kind == "latent_attention":
-            self._latent_attention(li, m, P, proj, mix, rows, views)
+            self._latent_attention(li, m, P, proj, mix, rows, views, tiles)
         elif m.kind == "mamba2":
             self._mamba2(li, m, P, proj, mix, rows, views)
         else:
@@ -653,25 +665,48 @@ class RaggedEngine:
         self._lin(act, P["w_down"], y2)
         ops.residual_add2(x, y, y2, idw if e.identity else None, hn if e.identity else None)
 
-    def _latent_attention(self, li, m, P, proj, mix, rows, views):
-        """Attention over the cached latents: the heads' key up-projections are folded into the queries, the value
-        up-projections applied to the attention output (one shared key/value row per position)."""
+    def _latent_attention(self, li, m, P, proj, mix, rows, views, tiles=False):
+        """Decode rows and short portions: attention over the cached latents themselves — the heads' key up-projections
+        are folded into the queries, the value up-projections applied to the attention output (one shared key/value row
+        per position).  Steps with portions of prompts (tiles): the latents of the pages in use are expanded to per-head
+        keys and values by one GEMM and attention runs head by head on the tensor-core tiles."""
         d_tok, d_rent, d_ent, d_want, d_tiles = views
         pool = self.kv.k[self.kv_index[li]]
-        K, R, H = m.kv_rank, m.rot_dims, m.heads
+        K, R, H, D, V = m.kv_rank, m.rot_dims, m.heads, m.dim, m.vdim
         cos_t, sin_t = self._table(m.rot_base, R, None) if R else (None, None)
         cq = self._cq[:rows * m.q_rank].view(rows, m.q_rank)
         off = P["off"]
         ops.latent_prep(proj, cq, pool, d_rent, d_ent, self.kv.page_table, m.q_rank, K, R, off["cq"], off["kv"],
                         P["q_norm"], P["kv_norm"], self.spec.eps, cos_t, sin_t)
-        q = self._q[:rows * H * (m.dim + R)].view(rows, H * (m.dim + R))
+        q = self._q[:rows * H * (D + R)].view(rows, H * (D + R))
         self._lin(cq, P["w_uq"], q)
+        ps = self.kv.page_size
+        if tiles and "w_ukv" in P and m.scale > 0 and self._step_pages is not None and (K + R) % 8 == 0:
+            lo, hi = self._step_pages
+            n = (hi - lo + 1) * ps
+            need = n * H * (2 * D + R + 2 * V)
+            if need <= self.latent_expand_max_elems:
+                if getattr(self, "_lx", None) is None or self._lx.numel() < need:
+                    self._lx = torch.empty(need, dtype=self.dtype, device=self.device)
+                kvx = self._lx[:n * H * (D + V)].view(n, H * (D + V))
+                kx = self._lx[n * H * (D + V):n * H * (2 * D + R + V)].view(hi - lo + 1, H, ps, D + R)
+                vx = self._lx[n * H * (2 * D + R + V):need].view(hi - lo + 1, H, ps, V)
+                rows_pool = pool.view(-1, K + R)[lo * ps:(hi + 1) * ps]
+                self._lin(rows_pool, P["w_ukv"], kvx)
+                ops.latent_expand(kvx, rows_pool, kx, vx, H, D, R, V, K, ps)
+                qbuf = self._qbuf[:rows * H * (D + R)].view(rows, H * (D + R))
+                ops.latent_q_absorb(q, None, qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, D)
+                ops.attn_ragged_tc(qbuf, kx, vx, None, mix, d_ent, d_tiles, self.kv.page_table, H, H, D + R, V, m.scale,
+                                   page_base=lo)
+                if m.out_gate:
+                    ops.sigmoid_gate(mix, proj, off["g"])
+                return
         qbuf = self._qbuf[:rows * H * (K + R)].view(rows, H * (K + R))
-        ops.latent_q_absorb(q, P["uk"], qbuf, d_rent, d_ent, cos_t, sin_t, H, m.dim, R, K)
+        ops.latent_q_absorb(q, P["uk"], qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, K)
         olat = self._olat[:rows * H * K].view(rows, H * K)
         ops.attn_ragged(qbuf, pool, pool, None, olat, d_rent, d_ent, self.kv.page_table, H, 1, K + R, K, m.scale,
                         ldv=K + R)
-        ops.latent_v_up(olat, P["uv"], proj if m.out_gate else None, mix, H, m.vdim, K, g_off=off["g"])
+        ops.latent_v_up(olat, P["uv"], proj if m.out_gate else None, mix, H, V, K, g_off=off["g"])
 
     def _mamba2(self, li, m, P, proj, mix, rows, views):
         d_tok, d_rent, d_ent, d_want, d_tiles = views

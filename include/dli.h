@@ -498,6 +498,14 @@ int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_
                         dli_stream_t stream);
 int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, int rows, int H, int V, int K, int ldp,
                     int g_off, int dt, dli_stream_t stream);
+/* Steps with portions of prompts run latent attention head by head on the tensor cores instead: kv [n, H*D + H*V] =
+ * the up-projections of n consecutive pool rows (n a multiple of page_size), pool [n, K + R] those rows ->
+ * kx [n / page_size, H, page_size, D + R] = [k_n | k_r] and vx [.., V], the layout of dli_attn_ragged_tc;
+ * dli_latent_q_absorb with uk == NULL and K == D gives the matching queries [q_n | rot(q_r)];
+ * dli_sigmoid_gate: out[row, c] *= sigmoid(proj[row, g_off + c]). */
+int dli_latent_expand(const void* kv, const void* pool, void* kx, void* vx, int n, int H, int D, int R, int V, int K,
+                      int page_size, int dt, dli_stream_t stream);
+int dli_sigmoid_gate(void* out, const void* proj, int rows, int n, int ldp, int g_off, int dt, dli_stream_t stream);
 
 /* Selective state-space mixer (Mamba-2 form).  dli_conv1d_act_ragged: causal per-channel convolution (w [C, taps]
  * fp32, tap taps-1 is the current row; bias [C] or NULL; act 1 = SiLU) over columns [off, off + C) of proj, history

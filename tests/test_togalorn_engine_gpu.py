@@ -277,3 +277,33 @@ def test_decode_steps_replayed_as_a_graph_equal_eager_steps():
         if graph:
             assert any(isinstance(v, tuple) for v in eng._graphs.values())
     assert torch.equal(outs[0], outs[1])
+
+
+def test_bfloat16_portions_of_latent_attention_on_the_tensor_cores():
+    """Head sizes that have a tensor-core tile: steps with portions of 16 rows and more expand the cached latents to
+    per-head keys and values and take that kernel (also for the short entries beside them, and with the pages in use
+    starting anywhere in the pool), other steps attend over the latents themselves; both against the oracle and
+    against each other."""
+    cfg = config([(latent(heads=4, dim=32, rot_dim=32, vdim=64, kv_rank=64, q_rank=48, scale=0.125), None),
+                  (mamba(), moe()),
+                  (latent(heads=2, dim=64, rot_dim=64, vdim=128, kv_rank=96, q_rank=32, scale=0.09), moe())], width=128)
+    eng, sd = build(cfg, torch.bfloat16, max_seq_len=256, page_size=16, pool=512)
+    assert "w_ukv" in eng.layers[0] and "w_ukv" in eng.layers[2]
+    toks = prompt(170, cfg["vocab"], 6)
+    ref, _ = R.forward(cfg, sd, toks)
+    whole = run_schedule(eng, toks, [170])
+    hold = eng.open_sequence()                 # another sequence holds the first pages of the pool meanwhile
+    eng.step([(hold, prompt(40, cfg["vocab"], 7))])
+    parts = run_schedule(eng, toks, [70, 3, 64, 20])
+    eng.close_sequence(hold)
+    eng.tc_min_rows = 10 ** 9
+    rowwise = run_schedule(eng, toks, [170])
+    for got in (whole, parts, rowwise):
+        assert close16(rel_err(got, ref))
+    assert close16(rel_err(whole, rowwise.double()))
+    # a long portion beside a decoding sequence in one step
+    eng.tc_min_rows = 16
+    a, b = eng.open_sequence(), eng.open_sequence()
+    eng.step([(a, toks[:50])])
+    both = eng.step([(a, [toks[50]]), (b, toks[:90])], [[0], list(range(90))]).float().cpu()
+    assert close16(rel_err(both[:1], ref[50:51])) and close16(rel_err(both[1:], ref[:90]))
