@@ -506,6 +506,209 @@ def run_hybrid_compare(args, peaks):
     return out
 
 
+# ---------------------------------------------------------------------------------- Togalorn beside Sokevik
+def togalorn_config(width, heads, kv, hd, ff, layers, vocab):
+    """The Togalorn design at the sizes of a Llama layer: layers alternate state-space and latent-attention mixers (the
+    same head count and head size as the attention it is compared with: 64 unrotated + 64 rotated key dims, value
+    size hd, a 512-wide cached latent), every layer with a mixture of 8 experts of size ff/4 (2 per token) beside one
+    shared expert of size ff/2, so that a token uses as many feed-forward weights as the dense layer it is compared
+    with; the two layers run twice (a loop of two passes)."""
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": hd // 2, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 512, "q_rank": width // 2,
+                     "scale": hd ** -0.5, "rot": {"base": 500000.0, "dims": hd // 2}}}
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1,
+                                       "conv": 4}}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0}, "router": {"experts": 8, "identity": 1, "top": 2},
+           "shared": {"ff": ff // 2, "limit": 7.0}}
+    return {"architecture": "Togalorn", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "loop": {"start": 0, "stop": 2, "times": layers // 2},
+            "layers": [dict(ssm, mlp=mlp), dict(lat, mlp=mlp)]}
+
+
+def ragged_throughput(eng, vocab, T, K, W, batch, tag, flush):
+    """Prefill (one T-token portion, L2 flushed before) and decode (batch 1 and `batch`, context T) tokens/s of a
+    RaggedEngine, CUDA events."""
+    from dli_b200 import ops
+
+    res = {}
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, vocab, (T,), generator=g).tolist()
+
+    def prefill_once():
+        s = eng.open_sequence()
+        eng.step([(s, prompt)])
+        return s
+
+    for _ in range(2):
+        eng.close_sequence(prefill_once())
+    times = []
+    for _ in range(3):
+        flush.fill_(1)
+        slot = [None]
+        times.append(ev_time_ms(lambda: slot.__setitem__(0, prefill_once())))
+        eng.close_sequence(slot[0])
+    res[f"{tag}_prefill_tok_s"] = round(T / (statistics.median(times) / 1e3), 1)
+    res[f"{tag}_prefill_ms"] = round(statistics.median(times), 3)
+    for B in sorted({1, batch if batch > 1 else 8}):
+        slots = [prefill_once() for _ in range(B)]
+        step = lambda: eng.step([(s, [7]) for s in slots])  # noqa: E731
+        for _ in range(W):
+            step()
+        n0 = ops.launch_count
+        ms = ev_time_ms(lambda: [step() for _ in range(K)])
+        res[f"{tag}_decode_b{B}_tok_s"] = round(B * K / (ms / 1e3), 1)
+        res[f"{tag}_decode_b{B}_launches_per_step"] = (ops.launch_count - n0) // K
+        for s in slots:
+            eng.close_sequence(s)
+    res[f"{tag}_weight_gb"] = round(eng.weight_bytes() / 1e9, 3)
+    return res
+
+
+def run_togalorn_compare(args, peaks):
+    """Prefill and decode throughput of the Togalorn design beside the framework's closest model, the Sokevik design
+    (both on RaggedEngine), at equal layer sizes and depth, random weights, plus each kernel of the new mechanisms
+    alone against its roofline.  One JSON line; the default workload of this file is untouched."""
+    from dli_b200 import sokevik, togalorn
+    from dli_b200.ragged_engine import RaggedEngine
+
+    T, K, W = args.ctx, args.steps, args.warmup
+    out = {"metric": "togalorn_vs_sokevik", "unit": "tokens/s", "ctx": T, "steps": K, "warmup": W, "dtype": "bf16",
+           "data": "synthetic", "peaks": peaks, "sizes": {}}
+    names = args.hybrid_sizes.split(",")
+    if len(names) > 1:
+        import subprocess
+        for name in names:
+            cmd = [sys.executable, os.path.abspath(__file__), "--compare-togalorn", "--hybrid-sizes", name, "--steps", str(K),
+                   "--warmup", str(W), "--ctx", str(T), "--batch", str(args.batch), "--page-size", str(args.page_size)]
+            p = subprocess.run(cmd, capture_output=True, text=True, check=True)
+            out["sizes"].update(json.loads(p.stdout.strip().splitlines()[-1])["sizes"])
+        return out
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in names:
+        width, heads, kv, hd, ff, layers, vocab = HYBRID_SIZES[name]
+        mods = ((togalorn, togalorn_config(width, heads, kv, hd, ff, layers, vocab), "togalorn"),
+                (sokevik, hybrid_config(width, heads, kv, hd, ff, layers, vocab, chunk=T), "sokevik"))
+        res = {}
+        for mod, cfg, tag in mods:
+            spec = mod.spec_from_config(cfg)
+            eng = RaggedEngine(spec, max_batch=max(args.batch, 8), max_seq_len=T + K + W + 64, page_size=args.page_size)
+            eng.load_tensors(mod.model_tensors(spec, mod.random_state_dict(spec, seed=1, std=0.02, device="cuda")))
+            res.update(ragged_throughput(eng, vocab, T, K, W, args.batch, tag, flush))
+            res[f"{tag}_kernels"] = togalorn_kernel_times(eng, spec, T, peaks) if tag == "togalorn" else \
+                hybrid_kernel_times(eng, spec, T, peaks)
+            eng.unload()
+            del eng
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+    return out
+
+
+def togalorn_kernel_times(eng, spec, T, peaks):
+    """Each kernel of the Togalorn mechanisms alone at the step sizes of the comparison: a T-token portion (prefill) and
+    one token after T (decode), against its algorithmic HBM bytes or FLOPs and the measured peaks."""
+    from dli_b200 import ops
+
+    dev, E, W = eng.device, eng.dtype, spec.width
+    li_a = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "latent_attention")
+    li_s = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "mamba2")
+    hbm, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    res = {}
+
+    def timeit(fn, n=5, reps=10):
+        fn()
+        return statistics.median(ev_time_ms(lambda: [fn() for _ in range(reps)]) for _ in range(n)) / reps
+
+    def put(key, ms, byt=None, flops=None, fp32=None):
+        d = {"ms": round(ms, 4)}
+        if byt is not None:
+            d["of_hbm"] = round(byt / (ms / 1e3) / hbm, 3)
+        if flops is not None:
+            d["of_bf16_peak"] = round(flops / (ms / 1e3) / tc, 4)
+        if fp32 is not None:
+            d["tflops_fp32"] = round(fp32 / (ms / 1e3) / 1e12, 3)
+        res[key] = d
+
+    slot = eng.open_sequence()
+    eng.kv.reserve(slot, T + 1)
+    eng.kv.commit()
+    eb = 2
+    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
+        eng._workspace(rows)
+        row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ent = torch.tensor([slot, 0, rows, start], dtype=torch.int32, device=dev)
+        tiles = torch.tensor([[0, q0] for q0 in range(0, rows, 64)], dtype=torch.int32, device=dev)
+        views = (row_ent, row_ent, ent, row_ent, tiles)
+        eng._step_pages = (min(eng.kv.owned[slot]), max(eng.kv.owned[slot]))
+        x = torch.randn(rows, W, device=dev)
+        hn, he = torch.empty_like(x), torch.empty(rows, W, dtype=E, device=dev)
+        y1 = torch.randn(rows, W, device=dev).to(E)
+        P = eng.layers[li_a]
+        put(f"{tag}_group_rmsnorm", timeit(lambda: ops.group_rmsnorm(x, P["norm1"], spec.norm_groups, 1e-6, hn=hn, he=he)),
+            byt=rows * W * (4 + 4 + eb))
+        idw = torch.rand(rows, device=dev)
+        put(f"{tag}_residual_add2", timeit(lambda: ops.residual_add2(x, y1, y1, idw, hn)), byt=rows * W * (8 + 2 * eb + 4))
+        # latent attention: everything between the input projection and the output projection
+        m = spec.layers[li_a].mixer
+        proj = (0.5 * torch.randn(rows, P["w_proj"].shape[0], device=dev)).to(E)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        ms = timeit(lambda: eng._latent_attention(li_a, m, P, proj, mix, rows, views, rows > 1), n=3, reps=3)
+        if rows > 1:
+            fl = 2 * (rows * rows // 2) * m.heads * (m.dim + m.rot_dims + m.vdim) + \
+                2 * rows * (m.q_rank * m.heads * (m.dim + m.rot_dims) + m.kv_rank * m.heads * (m.dim + m.vdim))
+            put(f"{tag}_latent_attention_all", ms, flops=fl)
+        else:
+            byt = (start + 1) * (m.kv_rank + m.rot_dims) * eb + (P["w_uq"].numel() + P["uk"].numel() + P["uv"].numel()) * eb
+            put(f"{tag}_latent_attention_all", ms, byt=byt)
+        # state-space mixer: convolution, scan, gated norm
+        m, P = spec.layers[li_s].mixer, eng.layers[li_s]
+        inner, gn = m.heads * m.vdim, m.groups * m.state
+        C = inner + 2 * gn
+        proj = (0.5 * torch.randn(rows, P["w_proj"].shape[0], device=dev)).to(E)
+        xbc = torch.empty(rows, C, device=dev)
+        yss = torch.empty(rows, inner, device=dev)
+        mix = torch.empty(rows, inner, dtype=E, device=dev)
+        off = P["off"]
+        put(f"{tag}_ssm_conv", timeit(lambda: ops.conv1d_act_ragged(proj, eng.slots[("ctail", li_s)], P["conv_w"], P["conv_b"],
+                                                                    row_ent, ent, xbc, off["x"])), byt=rows * C * (eb + 4))
+        ms = timeit(lambda: ops.ssm_scan_ragged(xbc, proj, eng.slots[("S", li_s)], yss, ent, m.heads, m.vdim, m.state,
+                                                m.groups, off["dt"], P["dt_bias"], P["a_log"], P["d_skip"], blocked=rows > 1),
+                    n=3, reps=3)
+        if rows > 1:
+            # FMAs counted as 2: per 64-row block and head C.B^T (64*64*N), G.x (64*64*V), C.S and the state update (2*64*N*V)
+            put(f"{tag}_ssm_scan_blocked", ms, fp32=2 * rows * m.heads * (64 * m.state + 64 * m.vdim + 2 * m.state * m.vdim))
+            ms = timeit(lambda: ops.ssm_scan_ragged(xbc, proj, eng.slots[("S", li_s)], yss, ent, m.heads, m.vdim, m.state,
+                                                    m.groups, off["dt"], P["dt_bias"], P["a_log"], P["d_skip"]), n=2, reps=1)
+            put(f"{tag}_ssm_scan_token_by_token", ms, fp32=rows * m.heads * m.state * m.vdim * 5)
+        else:
+            put(f"{tag}_ssm_scan", ms, byt=2 * m.heads * m.state * m.vdim * 4)
+        put(f"{tag}_ssm_gated_norm", timeit(lambda: ops.gated_group_rmsnorm(yss, proj, P["out_norm"], mix, m.norm_groups, 1e-6,
+                                                                            off["z"])), byt=rows * inner * (4 + 2 * eb))
+        # mixture of experts: router, the activation between the two projections, the projections themselves
+        e = spec.layers[li_s].moe
+        wts, idw = torch.empty(rows, e.experts, device=dev), torch.empty(rows, device=dev)
+        si = torch.empty(rows, e.top, dtype=torch.int32, device=dev)
+        sw = torch.empty(rows, e.top, device=dev)
+        put(f"{tag}_moe_route", timeit(lambda: ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, si, sw, e.experts, e.top)),
+            byt=rows * W * 4 + P["w_router"].numel() * 4)
+        gu = torch.empty(rows, P["w_gu"].shape[0], dtype=E, device=dev)
+        act = torch.empty(rows, e.total_ff, dtype=E, device=dev)
+        y2 = torch.empty(rows, W, dtype=E, device=dev)
+        ms_gu = timeit(lambda: eng._lin(he, P["w_gu"], gu), n=3, reps=3)
+        ms_act = timeit(lambda: ops.moe_act(gu, wts, act, e.experts, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha))
+        ms_dn = timeit(lambda: eng._lin(act, P["w_down"], y2), n=3, reps=3)
+        put(f"{tag}_moe_act", ms_act, byt=rows * e.total_ff * 3 * eb)
+        if rows > 1:
+            used = 2 * rows * 3 * W * (e.top * e.ff + e.shared_ff)      # FLOPs of the experts a token uses
+            put(f"{tag}_moe_projections", ms_gu + ms_dn, flops=used)
+            res[f"{tag}_moe_projections"]["of_bf16_peak_all_experts"] = round(2 * rows * 3 * W * e.total_ff / ((ms_gu + ms_dn) / 1e3) / tc, 4)
+        else:
+            put(f"{tag}_moe_projections", ms_gu + ms_dn, byt=3 * W * (e.top * e.ff + e.shared_ff) * eb)
+            res[f"{tag}_moe_projections"]["of_hbm_all_experts"] = round(3 * W * e.total_ff * eb / ((ms_gu + ms_dn) / 1e3) / hbm, 3)
+    eng.close_sequence(slot)
+    return res
+
+
+
 def hybrid_kernel_times(eng, spec, T, peaks):
     """Each kernel of the ragged path alone at the step sizes of the comparison: a T-token portion (prefill) and one
     token after T (decode), against its algorithmic HBM bytes (or FLOPs) and the measured peaks."""
@@ -641,6 +844,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--compare-hybrid", action="store_true",
                     help="instead of the default workload: the layer-by-layer family beside the uniform stack at equal sizes")
+    ap.add_argument("--compare-togalorn", action="store_true",
+                    help="instead of the default workload: the Togalorn design beside the Sokevik design at equal sizes")
     ap.add_argument("--hybrid-sizes", default="1b,8b")
     args = ap.parse_args()
 
@@ -659,6 +864,10 @@ def main():
     if args.compare_hybrid:
         if rank == 0:
             print(json.dumps(run_hybrid_compare(args, peaks)), flush=True)
+        return
+    if args.compare_togalorn:
+        if rank == 0:
+            print(json.dumps(run_togalorn_compare(args, peaks)), flush=True)
         return
     if world > 1 or args.gpus > 1:
         from dli_b200.pipeline import run_pipeline_bench

@@ -80,9 +80,11 @@ SIGNATURES = {
     "dli_latent_expand": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_sigmoid_gate": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "dli_conv1d_act_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
-    "dli_ssm_scan_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
+    "dli_ssm_scan_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "dli_gated_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _vp]),
     "dli_moe_route": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "dli_moe_sel_supported": (_i, [_i, _i, _i, _i]),
+    "dli_moe_sel_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp]),
     "dli_moe_act": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _i, _f, _f, _i, _i, _vp]),
     "dli_scalar_rmsnorm_f32": (_i, [_vp, _vp, _i, _i, _f, _f, _vp]),
     "dli_postnorm_add_norm": (_i, [_vp, _vp, _vp, _i, _i, _f, _f, _f, _i, _vp]),
@@ -94,7 +96,7 @@ SIGNATURES = {
     "dli_attn_prep_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                   _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "dli_attn_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
-                             _i, _vp, _vp, _i, _i, _vp]),
+                             _i, _vp, _vp, _i, _i, _vp, _i, _vp]),
     "dli_attn_ragged_tc_supported": (_i, [_i, _i, _i]),
     "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
                                 _i, _vp, _vp, _vp]),

@@ -115,6 +115,8 @@ struct AttnRun {
   const float* sin_v;
   int ldv;                  // elements between the value rows of consecutive positions (V; the key size when the
                             // values are the leading part of the key rows of one shared pool)
+  int splits;               // > 1: the keys of a row are dealt to `splits` CTAs (grid.z), whose partial sums
+  float* part;              // [rows, H, splits, V + 2] (unnormalised output, maximum, denominator) a merge kernel adds
 };
 
 // q (shared, fp32) . k row (global): 16-byte loads where the row allows them
@@ -170,20 +172,27 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
   if (a.chunk > 0) lo = (pos / a.chunk) * a.chunk;
   if (a.window > 0 && pos - a.window + 1 > lo) lo = pos - a.window + 1;
   for (int c = tid; c < a.D; c += kAttnThreads) q[c] = qbuf[((size_t)row * a.H + h) * a.D + c] * a.scale;
+  int jb = lo, je = pos;    // this CTA's keys
+  if (a.splits > 1) {
+    const int per = (pos - lo + a.splits) / a.splits;
+    jb = lo + (int)blockIdx.z * per;
+    je = min(pos, jb + per - 1);
+  }
 
   const int groups = a.V >= kAttnThreads ? 1 : kAttnThreads / a.V;
   const int my_group = a.V >= kAttnThreads ? 0 : tid / a.V;
   const bool pv_active = my_group < groups;
   const int d0 = a.V >= kAttnThreads ? tid : tid % a.V;
   float acc[kAttnMaxVPerThread] = {0.f, 0.f, 0.f, 0.f};
-  float m = a.sink ? a.sink[h] : -INFINITY;  // the sink enters as a term exp(sink - m) = 1 of the denominator
-  float l = a.sink ? 1.f : 0.f;
+  const bool has_sink = a.sink && blockIdx.z == 0;
+  float m = has_sink ? a.sink[h] : -INFINITY;  // the sink enters as a term exp(sink - m) = 1 of the denominator
+  float l = has_sink ? 1.f : 0.f;
   __syncthreads();
 
-  for (int j0 = lo; j0 <= pos; j0 += kAttnThreads) {
+  for (int j0 = jb; j0 <= je; j0 += kAttnThreads) {
     const int j = j0 + tid;
     float s = -INFINITY;
-    if (j <= pos) {
+    if (j <= je) {
       const E* kr = kc + (((size_t)pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size) * a.D;
       s = dot_row(q, kr, a.D);
     }
@@ -195,25 +204,37 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     const float m_new = fmaxf(m, mx);
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    const float w = (j <= pos) ? expf(s - m_new) : 0.f;
+    const float w = (j <= je) ? expf(s - m_new) : 0.f;
     p[tid] = w;
     float ws = warp_sum(w);
     if ((tid & 31) == 0) red[4 + (tid >> 5)] = ws;
     __syncthreads();
     l = l * corr + (red[4] + red[5] + red[6] + red[7]);
     m = m_new;
-    const int cnt = min(kAttnThreads, pos - j0 + 1);
+    const int cnt = min(kAttnThreads, je - j0 + 1);
 #pragma unroll
     for (int i = 0; i < kAttnMaxVPerThread; ++i) acc[i] *= corr;
     if (pv_active) {
-      for (int jj = my_group; jj < cnt; jj += groups) {
-        const int jk = j0 + jj;
-        const E* vr = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.ldv;
-        const float wj = p[jj];
+      // four keys per round: their page lookups and value loads are all in flight before the first is used
+      for (int jj = my_group; jj < cnt; jj += 4 * groups) {
+        const E* vr[4];
+        float wj[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int ju = jj + u * groups, jk = j0 + min(ju, cnt - 1);
+          vr[u] = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.ldv;
+          wj[u] = ju < cnt ? p[ju] : 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < kAttnMaxVPerThread; ++i) {
           const int d = d0 + i * kAttnThreads;
-          if (d < a.V) acc[i] = fmaf(wj, a_to_f(vr[d]), acc[i]);
+          if (d < a.V) {
+            float f[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) f[u] = a_to_f(vr[u][d]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[i] = fmaf(wj[u], f[u], acc[i]);
+          }
         }
       }
     }
@@ -228,6 +249,16 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     }
   }
   __syncthreads();
+  if (a.splits > 1) {
+    float* pr = a.part + (((size_t)row * a.H + h) * a.splits + blockIdx.z) * (a.V + 2);
+    for (int d = tid; d < a.V; d += kAttnThreads) {
+      float u = 0.f;
+      for (int gg = 0; gg < groups; ++gg) u += ov[gg * a.V + d];
+      pr[d] = u;
+    }
+    if (tid == 0) { pr[a.V] = m; pr[a.V + 1] = l; }
+    return;
+  }
   float gate = 1.f;
   if (a.g_off >= 0) gate = 1.f / (1.f + expf(-a_to_f(proj[(size_t)row * a.ldp + a.g_off + h])));
   const float inv = 1.f / l;
@@ -239,6 +270,59 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     if (a.cos_v) {
       const float c = a.cos_v[(size_t)pos * (a.V / 2) + i], s = a.sin_v[(size_t)pos * (a.V / 2) + i];
       const float u2 = u * c + v * s, v2 = v * c - u * s;  // by -angle
+      u = u2; v = v2;
+    }
+    orow[2 * i] = a_from_f<E>(u * gate);
+    orow[2 * i + 1] = a_from_f<E>(v * gate);
+  }
+}
+
+// Adds the partial sums of a row's key splits: o = sum_z e^(m_z - M) o_z / sum_z e^(m_z - M) l_z, then the same
+// epilogue (turn back, gate).  One CTA per (row, head).
+template <typename E>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_ragged_merge_kernel(const E* __restrict__ proj, E* __restrict__ out, AttnRun a) {
+  __shared__ float wz[64];   // e^(m_z - M) per split (0 for an empty split)
+  __shared__ float lz[64];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const float* pr = a.part + ((size_t)row * a.H + h) * a.splits * (a.V + 2);
+  if (tid < 64) {
+    wz[tid] = tid < a.splits ? pr[(size_t)tid * (a.V + 2) + a.V] : -INFINITY;
+    lz[tid] = tid < a.splits ? pr[(size_t)tid * (a.V + 2) + a.V + 1] : 0.f;
+  }
+  __syncthreads();
+  float M = -INFINITY;
+  for (int z = 0; z < a.splits; ++z) M = fmaxf(M, wz[z]);
+  __syncthreads();
+  if (tid < 64) wz[tid] = wz[tid] == -INFINITY ? 0.f : expf(wz[tid] - M);
+  __syncthreads();
+  float L = 0.f;
+  for (int z = 0; z < a.splits; ++z) L += wz[z] * lz[z];
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[a.row_ent[row]];
+  const int pos = e.w + (row - e.y);
+  float gate = 1.f;
+  if (a.g_off >= 0) gate = 1.f / (1.f + expf(-a_to_f(proj[(size_t)row * a.ldp + a.g_off + h])));
+  const float inv = 1.f / L;
+  E* orow = out + ((size_t)row * a.H + h) * a.V;
+  for (int i = tid; i < a.V / 2; i += kAttnThreads) {
+    float u = 0.f, v = 0.f;
+    for (int z0 = 0; z0 < a.splits; z0 += 8) {  // eight splits' loads in flight together
+      float2 f[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int z = min(z0 + k, a.splits - 1);
+        f[k] = *reinterpret_cast<const float2*>(pr + (size_t)z * (a.V + 2) + 2 * i);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (z0 + k < a.splits) { u = fmaf(wz[z0 + k], f[k].x, u); v = fmaf(wz[z0 + k], f[k].y, v); }
+    }
+    u *= inv; v *= inv;
+    if (a.cos_v) {
+      const float c = a.cos_v[(size_t)pos * (a.V / 2) + i], s = a.sin_v[(size_t)pos * (a.V / 2) + i];
+      const float u2 = u * c + v * s, v2 = v * c - u * s;
       u = u2; v = v2;
     }
     orow[2 * i] = a_from_f<E>(u * gate);
@@ -487,8 +571,10 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
-                    int g_off, const float* cos_v, const float* sin_v, int ldv, int dt, dli_stream_t stream) {
+                    int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
+                    dli_stream_t stream) {
   DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && row_ent && ent && page_table, "dli_attn_ragged: null pointer");
+  DLI_CHECK_ARG(splits >= 1 && splits <= 64 && (splits == 1 || part), "dli_attn_ragged: %d key splits (1..64, with scratch)", splits);
   DLI_CHECK_ARG(ldv == 0 || ldv >= V, "dli_attn_ragged: value row stride %d is below the value size %d", ldv, V);
   DLI_CHECK_ARG(g_off < 0 || proj, "dli_attn_ragged: a gate needs the projection rows");
   DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0 && V % 2 == 0 && V <= kAttnThreads * kAttnMaxVPerThread,
@@ -497,13 +583,17 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v,
-            ldv ? ldv : V};
+            ldv ? ldv : V, splits, part};
   const int groups = V >= kAttnThreads ? 1 : kAttnThreads / V;
   const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
   DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("attn_ragged", attn_ragged_kernel<bf16>, dim3(rows, H), dim3(kAttnThreads), smem, s, qbuf, (const bf16*)k_cache, (const bf16*)v_cache, (const bf16*)proj, (bf16*)out, a);
-  else DLI_LAUNCH("attn_ragged", attn_ragged_kernel<float>, dim3(rows, H), dim3(kAttnThreads), smem, s, qbuf, (const float*)k_cache, (const float*)v_cache, (const float*)proj, (float*)out, a);
+  if (dt == 0) DLI_LAUNCH("attn_ragged", attn_ragged_kernel<bf16>, dim3(rows, H, splits), dim3(kAttnThreads), smem, s, qbuf, (const bf16*)k_cache, (const bf16*)v_cache, (const bf16*)proj, (bf16*)out, a);
+  else DLI_LAUNCH("attn_ragged", attn_ragged_kernel<float>, dim3(rows, H, splits), dim3(kAttnThreads), smem, s, qbuf, (const float*)k_cache, (const float*)v_cache, (const float*)proj, (float*)out, a);
+  if (splits > 1) {
+    if (dt == 0) DLI_LAUNCH("attn_ragged_merge", attn_ragged_merge_kernel<bf16>, dim3(rows, H), dim3(kAttnThreads), 0, s, (const bf16*)proj, (bf16*)out, a);
+    else DLI_LAUNCH("attn_ragged_merge", attn_ragged_merge_kernel<float>, dim3(rows, H), dim3(kAttnThreads), 0, s, (const float*)proj, (float*)out, a);
+  }
   return DLI_OK;
 }
 
@@ -522,7 +612,7 @@ int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cac
   if (!dli_attn_ragged_tc_supported(D, V, 0))
     return dli::fail(DLI_ERR_UNSUPPORTED, "dli_attn_ragged_tc: key size %d with value size %d has no tensor-core tile", D, V);
   if (n_tiles <= 0) return DLI_OK;
-  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v, V};
+  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v, V, 1, nullptr};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 64 && V == 64) return launch_ragged_tc<64, 64>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
   if (D == 128 && V == 128) return launch_ragged_tc<128, 128>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);

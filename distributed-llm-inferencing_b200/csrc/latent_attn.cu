@@ -101,7 +101,7 @@ latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float*
   }
   __syncthreads();
   const E* w = uk + (size_t)h * D * K;
-  for (int k = tid; k < K; k += blockDim.x) {
+  for (int k = blockIdx.z * blockDim.x + tid; k < K; k += blockDim.x * gridDim.z) {
     if (uk == nullptr) {  // no folding: K == D, the unrotated part passes through
       for (int r = 0; r < nr; ++r) qbuf[((size_t)(r0 + r) * H + h) * (K + R) + k] = qs[r * D + k];
       continue;
@@ -118,6 +118,7 @@ latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float*
     for (int r = 0; r < kLatRows; ++r)
       if (r < nr) qbuf[((size_t)(r0 + r) * H + h) * (K + R) + k] = acc[r];
   }
+  if (blockIdx.z != 0) return;
   for (int i = tid; i < nr * (R / 2); i += blockDim.x) {
     const int r = i / (R / 2), p = i - r * (R / 2);
     const int row = r0 + r;
@@ -148,7 +149,7 @@ latent_v_up_kernel(const E* __restrict__ o, const E* __restrict__ uv, const E* _
     os[i] = r < nr ? l_to_f(o[((size_t)(r0 + r) * H + h) * K + k]) : 0.f;
   }
   __syncthreads();
-  for (int v = warp; v < V; v += nw) {
+  for (int v = blockIdx.z * nw + warp; v < V; v += nw * gridDim.z) {
     const E* w = uv + ((size_t)h * V + v) * K;
     float acc[kLatRows];
 #pragma unroll
@@ -242,9 +243,10 @@ int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid((rows + kLatRows - 1) / kLatRows, H);
-  const size_t smem = (size_t)kLatRows * D * sizeof(float);
   const int th = K >= 256 ? 256 : 128;
+  // few rows (decode): a head's outputs are dealt to several CTAs so that the up-projection is read by many SMs
+  const dim3 grid((rows + kLatRows - 1) / kLatRows, H, rows <= 16 ? (K + th - 1) / th : 1);
+  const size_t smem = (size_t)kLatRows * D * sizeof(float);
   if (dt == 0) DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<bf16>, grid, dim3(th), smem, s, (const bf16*)q, (const bf16*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K);
   else DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<float>, grid, dim3(th), smem, s, (const float*)q, (const float*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K);
   return DLI_OK;
@@ -258,7 +260,7 @@ int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, 
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid((rows + kLatRows - 1) / kLatRows, H);
+  const dim3 grid((rows + kLatRows - 1) / kLatRows, H, rows <= 16 ? (V + 31) / 32 : 1);
   const size_t smem = (size_t)kLatRows * K * sizeof(float);
   if (dt == 0) DLI_LAUNCH("latent_v_up", latent_v_up_kernel<bf16>, grid, dim3(256), smem, s, (const bf16*)o, (const bf16*)uv, (const bf16*)proj, (bf16*)out, rows, H, V, K, ldp, g_off);
   else DLI_LAUNCH("latent_v_up", latent_v_up_kernel<float>, grid, dim3(256), smem, s, (const float*)o, (const float*)uv, (const float*)proj, (float*)out, rows, H, V, K, ldp, g_off);

@@ -45,7 +45,7 @@ conv1d_act_kernel(const E* __restrict__ proj, const float* __restrict__ tail, co
   const int row = blockIdx.x;
   const int4 e = reinterpret_cast<const int4*>(ent)[row_ent[row]];  // slot, row0, n, start
   const int back = row - e.y, pos = e.w + back;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += blockDim.x * gridDim.y) {
     float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int dist = taps - 1 - j;
@@ -69,7 +69,7 @@ conv1d_tail_kernel(const E* __restrict__ proj, float* __restrict__ tail, const i
   pdl_trigger();
   const int4 e = reinterpret_cast<const int4*>(ent)[blockIdx.x];
   const int keep = taps - 1, end = e.w + e.z;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += blockDim.x * gridDim.y) {
     float* t = tail + (size_t)e.x * keep * C + c;
     for (int i = 0; i < keep; ++i) {  // ascending: slot i reads old slot i + n (n >= 1), never one already written
       const int p = end - keep + i;
@@ -148,6 +148,171 @@ ssm_scan_kernel(const float* __restrict__ xbc, const E* __restrict__ proj, float
   }
 }
 
+
+// ---- the same recurrence 64 rows at a time (steps with portions of prompts) -------------------------------------
+// With a_t = -exp(A_log) dt_t and c_t = a_1 + .. + a_t inside a block that starts from state S_in:
+//   y_t   = exp(c_t) C_t^T S_in + sum_{s<=t} exp(c_t - c_s) dt_s (C_t . B_s) x_s + D x_t
+//   S_out = exp(c_L) S_in + sum_s exp(c_L - c_s) dt_s B_s x_s^T
+// Every exponent is <= 0, so nothing needs rescaling.  One CTA per (entry, head) walks the entry's blocks in order
+// with the state in shared memory; each block is four small fp32 matrix products on 64 x 64 output tiles, 4 x 4
+// outputs per thread (thread (r, c) owns rows r + 16 i and columns c + 16 j: conflict-free shared-memory reads).
+constexpr int kSsmL = 64;
+
+static inline size_t ssm_blocked_smem_bytes(int N, int V) {
+  return sizeof(float) * ((size_t)2 * kSsmL * (N + 1) + (size_t)kSsmL * V + (size_t)N * V + (size_t)kSsmL * (kSsmL + 1) + 3 * kSsmL);
+}
+
+template <typename E>
+__global__ void __launch_bounds__(256)
+ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ proj, float* __restrict__ S,
+                        float* __restrict__ y, SsmRun a) {
+  extern __shared__ float sm[];
+  const int N = a.N, V = a.V, NP = N + 1, LP = kSsmL + 1;
+  float* Bs = sm;                       // [L][N+1]
+  float* Cs = Bs + kSsmL * NP;          // [L][N+1]
+  float* Xs = Cs + kSsmL * NP;          // [L][V]
+  float* St = Xs + kSsmL * V;           // [N][V]
+  float* Gs = St + N * V;               // [L][L+1]
+  float* cum = Gs + kSsmL * LP;         // [L] running sum of a_t
+  float* dts = cum + kSsmL;             // [L]
+  float* wl = dts + kSsmL;              // [L] exp(c_L - c_s) dt_s
+  pdl_wait();
+  pdl_trigger();
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[blockIdx.x];  // slot, row0, n, start
+  const int h = blockIdx.y, g = h / (a.H / a.G), tid = threadIdx.x;
+  const int tr = tid >> 4, tc = tid & 15;
+  const int inner = a.H * V;
+  float* Sp = S + (((size_t)e.x * a.H + h) * N) * V;
+  for (int i = tid; i < N * V; i += 256) St[i] = e.w > 0 ? Sp[i] : 0.f;
+  const float na = -expf(a.a_log[h]), db = a.dt_bias[h], dk = a.d_skip[h];
+  for (int b0 = 0; b0 < e.z; b0 += kSsmL) {
+    const int nb = min(kSsmL, e.z - b0);
+    __syncthreads();  // the previous block's reads of Bs, Cs, Xs, Gs are done; St is complete
+    for (int i = tid; i < kSsmL * N; i += 256) {
+      const int t = i / N, n = i - t * N;
+      const float* xr = xbc + (size_t)(e.y + b0 + t) * a.ldx + inner;
+      Bs[t * NP + n] = t < nb ? xr[g * N + n] : 0.f;
+      Cs[t * NP + n] = t < nb ? xr[a.G * N + g * N + n] : 0.f;
+    }
+    for (int i = tid; i < kSsmL * V; i += 256) {
+      const int t = i / V, v = i - t * V;
+      Xs[i] = t < nb ? xbc[(size_t)(e.y + b0 + t) * a.ldx + h * V + v] : 0.f;
+    }
+    if (tid < kSsmL) {
+      float dt = 0.f;
+      if (tid < nb) {
+        const float draw = m_to_f(proj[(size_t)(e.y + b0 + tid) * a.ldp + a.dt_off + h]) + db;
+        dt = draw > 20.f ? draw : log1pf(expf(draw));
+      }
+      dts[tid] = dt;
+      cum[tid] = na * dt;
+    }
+    __syncthreads();
+    if (tid == 0) {  // 64 additions in order: the same sums whatever the block's length
+      float c = 0.f;
+      for (int t = 0; t < kSsmL; ++t) { c += cum[t]; cum[t] = c; }
+    }
+    __syncthreads();
+    if (tid < kSsmL) wl[tid] = expf(cum[kSsmL - 1] - cum[tid]) * dts[tid];
+    // G[t][s] = (C_t . B_s) exp(c_t - c_s) dt_s for s <= t
+    {
+      float acc[4][4] = {};
+      for (int k = 0; k < N; ++k) {
+        float cv[4], bv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cv[i] = Cs[(tr + 16 * i) * NP + k];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[j] = Bs[(tc + 16 * j) * NP + k];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(cv[i], bv[j], acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int t = tr + 16 * i, s2 = tc + 16 * j;
+          Gs[t * LP + s2] = s2 <= t ? acc[i][j] * expf(cum[t] - cum[s2]) * dts[s2] : 0.f;
+        }
+    }
+    __syncthreads();
+    // y[t][v] = sum_s G[t][s] x[s][v] + exp(c_t) sum_n C[t][n] S[n][v] + D x[t][v]
+    for (int v0 = 0; v0 < V; v0 += 64) {
+      float acc[4][4] = {}, acs[4][4] = {};
+      int vv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) vv[j] = min(v0 + tc + 16 * j, V - 1);
+      for (int k = 0; k < kSsmL; ++k) {
+        float gv[4], xv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gv[i] = Gs[(tr + 16 * i) * LP + k];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xv[j] = Xs[k * V + vv[j]];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(gv[i], xv[j], acc[i][j]);
+      }
+      for (int k = 0; k < N; ++k) {
+        float cv[4], sv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cv[i] = Cs[(tr + 16 * i) * NP + k];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sv[j] = St[k * V + vv[j]];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acs[i][j] = fmaf(cv[i], sv[j], acs[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = tr + 16 * i;
+        if (t >= nb) continue;
+        const float ec = expf(cum[t]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int v = v0 + tc + 16 * j;
+          if (v < V) y[(size_t)(e.y + b0 + t) * inner + h * V + v] = acc[i][j] + ec * acs[i][j] + dk * Xs[t * V + v];
+        }
+      }
+    }
+    __syncthreads();  // every read of the incoming state is done
+    // S[n][v] = exp(c_L) S[n][v] + sum_s wl[s] B[s][n] x[s][v]
+    const float eL = expf(cum[kSsmL - 1]);
+    for (int n0 = 0; n0 < N; n0 += 64)
+      for (int v0 = 0; v0 < V; v0 += 64) {
+        float acc[4][4] = {};
+        int nn[4], vv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) nn[i] = min(n0 + tr + 16 * i, N - 1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) vv[j] = min(v0 + tc + 16 * j, V - 1);
+        for (int k = 0; k < kSsmL; ++k) {
+          const float w = wl[k];
+          float bv[4], xv[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) bv[i] = Bs[k * NP + nn[i]] * w;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xv[j] = Xs[k * V + vv[j]];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(bv[i], xv[j], acc[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tr + 16 * i, v = v0 + tc + 16 * j;
+            if (n < N && v < V) St[n * V + v] = eL * St[n * V + v] + acc[i][j];
+          }
+      }
+  }
+  __syncthreads();
+  for (int i = tid; i < N * V; i += 256) Sp[i] = St[i];
+}
+
 // out[row] = groupnorm(y[row] * silu(z[row])) * w; z = columns [z_off, z_off + d) of proj.
 template <typename E>
 __global__ void __launch_bounds__(1024)
@@ -192,24 +357,40 @@ int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const f
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("conv1d_act", conv1d_act_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
-  else DLI_LAUNCH("conv1d_act", conv1d_act_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
+  // few rows (decode): the channels of a row are dealt to several CTAs
+  const int gy = rows <= 64 ? (C + 255) / 256 : 1, gyt = n_ent <= 64 ? (C + 255) / 256 : 1;
+  if (dt == 0) DLI_LAUNCH("conv1d_act", conv1d_act_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, (const bf16*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
+  else DLI_LAUNCH("conv1d_act", conv1d_act_kernel<float>, dim3(rows, gy), dim3(256), 0, s, (const float*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
   if (taps > 1) {
-    if (dt == 0) DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<bf16>, dim3(n_ent), dim3(256), 0, s, (const bf16*)proj, tail, ent, C, taps, ldp, off);
-    else DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<float>, dim3(n_ent), dim3(256), 0, s, (const float*)proj, tail, ent, C, taps, ldp, off);
+    if (dt == 0) DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<bf16>, dim3(n_ent, gyt), dim3(256), 0, s, (const bf16*)proj, tail, ent, C, taps, ldp, off);
+    else DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<float>, dim3(n_ent, gyt), dim3(256), 0, s, (const float*)proj, tail, ent, C, taps, ldp, off);
   }
   return DLI_OK;
 }
 
 int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, const int32_t* ent, int n_ent, int H, int V,
                         int N, int G, int ldp, int dt_off, const float* dt_bias, const float* a_log, const float* d_skip,
-                        int dt, dli_stream_t stream) {
+                        int blocked, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(xbc && proj && S && y && ent && dt_bias && a_log && d_skip, "dli_ssm_scan_ragged: null pointer");
   DLI_CHECK_ARG(H > 0 && V > 0 && N > 0 && G > 0 && H % G == 0 && N <= 32 * kSsmMaxPerThread,
                 "dli_ssm_scan_ragged: H=%d V=%d N=%d G=%d (H %% G == 0, N <= %d)", H, V, N, G, 32 * kSsmMaxPerThread);
   DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_ssm_scan_ragged: ent must be 16-byte aligned");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (n_ent <= 0) return DLI_OK;
+  const size_t bsmem = ssm_blocked_smem_bytes(N, V);
+  if (blocked && bsmem <= 200 * 1024) {
+    SsmRun b{ent, H, V, N, G, H * V + 2 * G * N, ldp, dt_off, dt_bias, a_log, d_skip, 0, 0};
+    cudaStream_t bs = static_cast<cudaStream_t>(stream);
+    static PerDeviceOnce once_b, once_f;
+    if (dt == 0) {
+      DLI_ONCE_PER_DEVICE(once_b, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(ssm_scan_blocked_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
+      DLI_LAUNCH("ssm_scan_blocked", ssm_scan_blocked_kernel<bf16>, dim3(n_ent, H), dim3(256), bsmem, bs, xbc, (const bf16*)proj, S, y, b);
+    } else {
+      DLI_ONCE_PER_DEVICE(once_f, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(ssm_scan_blocked_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
+      DLI_LAUNCH("ssm_scan_blocked", ssm_scan_blocked_kernel<float>, dim3(n_ent, H), dim3(256), bsmem, bs, xbc, (const float*)proj, S, y, b);
+    }
+    return DLI_OK;
+  }
   int np = 1;
   while (np * kSsmMaxPerThread < N) np <<= 1;
   // few value columns per CTA: a scan is one dependent chain per entry and head, so the columns are what spreads it

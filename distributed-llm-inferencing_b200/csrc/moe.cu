@@ -101,7 +101,7 @@ struct MoeAct {
   int ld;                   // row stride of gu
 };
 
-// act[row, e*ff + f] and act[row, n_exp*ff + f] (shared); one CTA per row.
+// act[row, e*ff + f] and act[row, n_exp*ff + f] (shared); a row's channels go to one CTA, or to several for few rows.
 template <typename E>
 __global__ void __launch_bounds__(256)
 moe_act_kernel(const E* __restrict__ gu, const float* __restrict__ wts, E* __restrict__ act, MoeAct a) {
@@ -111,7 +111,7 @@ moe_act_kernel(const E* __restrict__ gu, const float* __restrict__ wts, E* __res
   const E* g = gu + row * a.ld;
   const int F = a.n_exp * a.ff + a.ff_s;
   E* out = act + row * F;
-  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < F; i += blockDim.x * gridDim.y) {
     float gv, uv, lim, wt;
     if (i < a.n_exp * a.ff) {
       const int e = i / a.ff, f = i - e * a.ff;
@@ -131,6 +131,94 @@ moe_act_kernel(const E* __restrict__ gu, const float* __restrict__ wts, E* __res
     uv = fminf(fmaxf(uv, -lim), lim);
     const float y = gv / (1.f + expf(-a.alpha * gv)) * (uv + 1.f);
     out[i] = x_from_f<E>(y * wt);
+  }
+}
+
+
+// ---- few rows (decode): only the chosen experts' weights are read ------------------------------------------------
+// dli_moe_sel_act: for row r and its k-th choice e = sel_idx[r, k] (k == top: the shared expert) the gate and up
+// rows of that expert are streamed (one warp per output, 16-byte loads) and the weighted activation goes to the
+// compact act_sel [rows, top*ff + ff_s] (zeros for a pass-through choice).  dli_moe_sel_down: y[r, c] = sum over the
+// choices of act_sel[r, k, :] . w_down[c, e_k*ff : +ff] plus the shared block.
+__device__ __forceinline__ float dot8(const uint4& w, const float* x) {
+  float f[8];
+  unpack8(w, f);
+  float a = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a = fmaf(f[j], x[j], a);
+  return a;
+}
+
+constexpr int kSelWarps = 8;
+constexpr int kSelPerWarp = 8;  // outputs per warp
+
+__global__ void __launch_bounds__(kSelWarps * 32)
+moe_sel_act_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_gu, const int32_t* __restrict__ sel_idx,
+                   const float* __restrict__ sel_w, bf16* __restrict__ act_sel, int d, int top, MoeAct a) {
+  extern __shared__ float xs[];  // [d]
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, k = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool shared = k == top;
+  const int ff = shared ? a.ff_s : a.ff;
+  const int f0 = (blockIdx.z * kSelWarps + warp) * kSelPerWarp;
+  if (blockIdx.z * kSelWarps * kSelPerWarp >= ff) return;
+  bf16* out = act_sel + (size_t)row * (top * a.ff + a.ff_s) + (shared ? top * a.ff : k * a.ff);
+  const int e = shared ? a.n_exp : sel_idx[row * top + k];
+  if (!shared && e >= a.n_exp) {  // a pass-through choice: nothing to stream
+    for (int f = f0 + lane; f < min(f0 + kSelPerWarp, ff); f += 32) out[f] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  for (int c = threadIdx.x; c < d; c += blockDim.x) xs[c] = __bfloat162float(x[(size_t)row * d + c]);
+  __syncthreads();
+  const float wt = shared ? 1.f : sel_w[row * top + k];
+  const float lim = shared ? a.limit_s : a.limit;
+  const bf16* base = w_gu + (size_t)e * 2 * a.ff * d;  // the shared expert's block follows the n_exp routed ones
+  for (int f = f0; f < min(f0 + kSelPerWarp, ff); ++f) {
+    const bf16* gr = base + (size_t)f * d;
+    const bf16* ur = base + (size_t)(ff + f) * d;
+    float g = 0.f, u = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+      g += dot8(ld_stream_16B(gr + c), xs + c);
+      u += dot8(ld_stream_16B(ur + c), xs + c);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+      g = __bfloat162float(__float2bfloat16_rn(g));  // the projection's output is a bf16 row, as on the dense path
+      u = __bfloat162float(__float2bfloat16_rn(u));
+      g = fminf(g, lim);
+      u = fminf(fmaxf(u, -lim), lim);
+      out[f] = __float2bfloat16_rn(g / (1.f + expf(-a.alpha * g)) * (u + 1.f) * wt);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kSelWarps * 32)
+moe_sel_down_kernel(const bf16* __restrict__ act_sel, const bf16* __restrict__ w_down, const int32_t* __restrict__ sel_idx,
+                    bf16* __restrict__ y, int d, int top, MoeAct a) {
+  extern __shared__ float as[];  // [top*ff + ff_s]
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_sel = top * a.ff + a.ff_s, F = a.n_exp * a.ff + a.ff_s;
+  for (int i = threadIdx.x; i < n_sel; i += blockDim.x) as[i] = __bfloat162float(act_sel[(size_t)row * n_sel + i]);
+  __syncthreads();
+  const int c0 = (blockIdx.y * kSelWarps + warp) * kSelPerWarp;
+  for (int c = c0; c < min(c0 + kSelPerWarp, d); ++c) {
+    const bf16* wr = w_down + (size_t)c * F;
+    float acc = 0.f;
+    for (int k = 0; k <= top; ++k) {
+      const bool shared = k == top;
+      const int e = shared ? a.n_exp : sel_idx[row * top + k];
+      if (!shared && e >= a.n_exp) continue;
+      const int ff = shared ? a.ff_s : a.ff;
+      const bf16* seg = wr + (size_t)e * a.ff;  // the shared block starts at n_exp * ff
+      const float* av = as + (shared ? top * a.ff : k * a.ff);
+      for (int f = lane * 8; f < ff; f += 256) acc += dot8(ld_stream_16B(seg + f), av + f);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[(size_t)row * d + c] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -160,8 +248,34 @@ int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp
   if (rows <= 0) return DLI_OK;
   MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, ld};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("moe_act", moe_act_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)gu, wts, (bf16*)act, a);
-  else DLI_LAUNCH("moe_act", moe_act_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)gu, wts, (float*)act, a);
+  const int gy = rows <= 64 ? min(64, (n_exp * ff + ff_s + 255) / 256) : 1;  // few rows: a row's channels over several CTAs
+  if (dt == 0) DLI_LAUNCH("moe_act", moe_act_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, (const bf16*)gu, wts, (bf16*)act, a);
+  else DLI_LAUNCH("moe_act", moe_act_kernel<float>, dim3(rows, gy), dim3(256), 0, s, (const float*)gu, wts, (float*)act, a);
+  return DLI_OK;
+}
+
+int dli_moe_sel_supported(int d, int ff, int ff_s, int top) {
+  return d % 8 == 0 && ff % 8 == 0 && ff_s % 8 == 0 && (size_t)d * 4 <= 96 * 1024 && ((size_t)top * ff + ff_s) * 4 <= 96 * 1024;
+}
+
+int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const int32_t* sel_idx, const float* sel_w,
+                     void* act_sel, void* y, int rows, int d, int n_exp, int top, int ff, float limit, int ff_s,
+                     float limit_s, float alpha, dli_stream_t stream) {
+  DLI_CHECK_ARG(x && w_gu && w_down && sel_idx && sel_w && act_sel && y, "dli_moe_sel_bf16: null pointer");
+  DLI_CHECK_ARG(n_exp >= 0 && top >= 0 && dli_moe_sel_supported(d, ff, ff_s, top) && aligned16(w_gu) && aligned16(w_down),
+                "dli_moe_sel_bf16: sizes d=%d ff=%d ff_s=%d must be multiples of 8 and fit shared memory", d, ff, ff_s);
+  if (rows <= 0) return DLI_OK;
+  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  static PerDeviceOnce once_a, once_d;
+  DLI_ONCE_PER_DEVICE(once_a, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(moe_sel_act_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)));
+  DLI_ONCE_PER_DEVICE(once_d, dev2, DLI_CUDA_CALL(cudaFuncSetAttribute(moe_sel_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)));
+  const int per = kSelWarps * kSelPerWarp;
+  const int ffm = ff > ff_s ? ff : ff_s;
+  DLI_LAUNCH("moe_sel_act", moe_sel_act_kernel, dim3(rows, top + (ff_s ? 1 : 0), (ffm + per - 1) / per), dim3(kSelWarps * 32),
+             (size_t)d * 4, s, (const bf16*)x, (const bf16*)w_gu, sel_idx, sel_w, (bf16*)act_sel, d, top, a);
+  DLI_LAUNCH("moe_sel_down", moe_sel_down_kernel, dim3(rows, (d + per - 1) / per), dim3(kSelWarps * 32),
+             ((size_t)top * ff + ff_s) * 4, s, (const bf16*)act_sel, (const bf16*)w_down, sel_idx, (bf16*)y, d, top, a);
   return DLI_OK;
 }
 

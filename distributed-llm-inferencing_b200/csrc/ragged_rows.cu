@@ -84,7 +84,7 @@ residual_add2_kernel(float* __restrict__ x, const E* __restrict__ y1, const E* _
   pdl_trigger();
   const size_t o = (size_t)blockIdx.x * d;
   const float aw = a ? a[blockIdx.x] : 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < d; c += blockDim.x * gridDim.y) {
     float v = to_f(y1[o + c]);
     if (y2) v += to_f(y2[o + c]);
     if (a) v += aw * h[o + c];
@@ -405,8 +405,9 @@ int dli_residual_add2(float* x, const void* y1, const void* y2, const float* a, 
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("residual_add2", residual_add2_kernel<bf16>, dim3(rows), dim3(256), 0, s, x, (const bf16*)y1, (const bf16*)y2, a, h, d);
-  else DLI_LAUNCH("residual_add2", residual_add2_kernel<float>, dim3(rows), dim3(256), 0, s, x, (const float*)y1, (const float*)y2, a, h, d);
+  const int gy = rows <= 64 ? (d + 1023) / 1024 : 1;
+  if (dt == 0) DLI_LAUNCH("residual_add2", residual_add2_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, x, (const bf16*)y1, (const bf16*)y2, a, h, d);
+  else DLI_LAUNCH("residual_add2", residual_add2_kernel<float>, dim3(rows, gy), dim3(256), 0, s, x, (const float*)y1, (const float*)y2, a, h, d);
   return DLI_OK;
 }
 

@@ -567,14 +567,17 @@ def attn_prep_append(proj, qbuf, k_cache, v_cache, row_ent, ent, page_table, H, 
 
 
 def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, G, D, V, scale, chunk=0, window=0,
-                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0):
+                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0, splits=1, part=None):
     """Chunk- / window-masked attention with an optional sink and output gate over the paged cache -> out [rows, H*V].
-    ldv: elements between value rows (0 = V); v_cache may be k_cache itself (values = leading part of the keys)."""
-    _f32(qbuf, sink, cos_v, sin_v), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
-    _call("dli_attn_ragged", 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(row_ent), _p(ent),
+    ldv: elements between value rows (0 = V); v_cache may be k_cache itself (values = leading part of the keys).
+    splits > 1: every row's keys are dealt to that many CTAs; part: float32 scratch of rows * H * splits * (V + 2)."""
+    _f32(qbuf, sink, cos_v, sin_v, part), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
+    if splits > 1 and part.numel() < qbuf.shape[0] * H * splits * (V + 2):
+        raise ValueError("attn_ragged: scratch too small for the key splits")
+    _call("dli_attn_ragged", 2 if splits > 1 else 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(row_ent), _p(ent),
           _p(page_table), page_table.shape[1], k_cache.shape[2], qbuf.shape[0], H, G, D, V, float(scale), int(chunk),
           int(window), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), int(ldv),
-          _dt(k_cache), _stream())
+          int(splits), _p(part), _dt(k_cache), _stream())
     return out
 
 
@@ -691,12 +694,12 @@ def conv1d_act_ragged(proj, tail, w, bias, row_ent, ent, out, off, act=1):
     return out
 
 
-def ssm_scan_ragged(xbc, proj, S, y, ent, H, V, N, G, dt_off, dt_bias, a_log, d_skip):
+def ssm_scan_ragged(xbc, proj, S, y, ent, H, V, N, G, dt_off, dt_bias, a_log, d_skip, blocked=False):
     """The state-space recurrence over the rows of every entry; S float32 [slots, H, N, V] is advanced; y float32
-    [rows, H*V]."""
+    [rows, H*V].  blocked: 64 rows at a time (steps with portions of prompts)."""
     _f32(xbc, S, y, dt_bias, a_log, d_skip), _req(proj, proj.dtype), _i32(ent)
     _call("dli_ssm_scan_ragged", 1, _p(xbc), _p(proj), _p(S), _p(y), _p(ent), ent.numel() // 4, H, V, N, G, proj.shape[1],
-          dt_off, _p(dt_bias), _p(a_log), _p(d_skip), _dt(proj), _stream())
+          dt_off, _p(dt_bias), _p(a_log), _p(d_skip), int(bool(blocked)), _dt(proj), _stream())
     return y
 
 
@@ -722,3 +725,15 @@ def moe_act(gu, wts, act, n_exp, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702):
     _call("dli_moe_act", 1, _p(gu), _p(wts), _p(act), gu.shape[0], int(n_exp), int(ff), float(limit), int(ff_s),
           float(limit_s), float(alpha), gu.shape[1], _dt(gu), _stream())
     return act
+
+
+def moe_sel_supported(d, ff, ff_s, top) -> bool:
+    return bool(_lib.load().dli_moe_sel_supported(int(d), int(ff), int(ff_s), int(top)))
+
+
+def moe_sel(x, w_gu, w_down, sel_idx, sel_w, act_sel, y, n_exp, top, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702):
+    """Few rows (decode): the chosen experts' and the shared expert's weights only -> y [rows, d] (bf16)."""
+    _req(x), _req(w_gu), _req(w_down), _req(act_sel), _req(y), _i32(sel_idx), _f32(sel_w)
+    _call("dli_moe_sel_bf16", 2, _p(x), _p(w_gu), _p(w_down), _p(sel_idx), _p(sel_w), _p(act_sel), _p(y), x.shape[0],
+          x.shape[1], int(n_exp), int(top), int(ff), float(limit), int(ff_s), float(limit_s), float(alpha), _stream())
+    return y

@@ -186,10 +186,12 @@ class RaggedEngine:
         self.pad_token_id: Optional[int] = None
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
         self.tc_min_rows = int(os.environ.get("DLI_RAGGED_TC_MIN_ROWS", "16"))  # portions from this size: tensor-core attention
+        self.moe_sel_max_rows = 8                  # up to this many rows a step reads only the chosen experts' weights
         self.latent_expand_max_elems = 1 << 31     # scratch bound (4 GiB in bf16) of the per-head expansion of cached latents
         self.mlstm_parallel_max_floats = 1 << 28   # scratch bound (1 GiB) of the block-parallel mLSTM; beyond it: blocks in order
         self.layer_trace: Optional[list] = None    # set to [] to collect the residual stream after every layer
         ops.set_pdl(os.environ.get("DLI_PDL", "1") == "1")
+        self._sms = ops.sm_count()
 
     # ------------------------------------------------------------------ weights
     def _table(self, base: float, dims: int, scaling: Optional[dict]):
@@ -337,7 +339,8 @@ class RaggedEngine:
         n_mix = max(m.heads * m.vdim for m in mx)
         n_q = max([m.heads * m.dim for m in mx if m.kind == "attention"] +
                   [m.heads * (max(m.kv_rank, m.dim) + m.rot_dims) for m in mx if m.kind == "latent_attention"] + [1])
-        ff = max([L.moe.total_ff if L.moe is not None else L.ff for L in s.layers] or [0])
+        ff = max([max(L.moe.total_ff, L.moe.top * L.moe.ff + L.moe.shared_ff) if L.moe is not None else L.ff
+                  for L in s.layers] or [0])
         n_gu = max([d["w_gu"].shape[0] for d in self.layers.values() if "w_gu" in d] or [1])
         f32 = torch.float32
         self._x = torch.empty(rows, s.width, dtype=f32, device=dev)
@@ -355,6 +358,9 @@ class RaggedEngine:
             self._cq = torch.empty(rows * max(m.q_rank for m in lat), dtype=E, device=dev)
             self._q = torch.empty(rows * max(m.heads * (m.dim + m.rot_dims) for m in lat), dtype=E, device=dev)
             self._olat = torch.empty(rows * max(m.heads * m.kv_rank for m in lat), dtype=E, device=dev)
+            # partial sums of the key splits of decode rows (rows * heads * splits <= 8 * SMs + rows * heads)
+            self._apart = torch.empty((8 * self._sms + 16 * max(m.heads for m in lat)) * (max(m.kv_rank for m in lat) + 2),
+                                      dtype=f32, device=dev)
         ssm = [m for m in mx if m.kind == "mamba2"]
         if ssm:
             self._xbc = torch.empty(rows * max(m.heads * m.vdim + 2 * m.groups * m.state for m in ssm), dtype=f32, device=dev)
@@ -644,7 +650,7 @@ class RaggedEngine:
         if m.kind == "latent_attention":
             self._latent_attention(li, m, P, proj, mix, rows, views, tiles)
         elif m.kind == "mamba2":
-            self._mamba2(li, m, P, proj, mix, rows, views)
+            self._mamba2(li, m, P, proj, mix, rows, views, long_step)
         else:
             raise ValueError(f"layer {li}: mixer {m.kind!r} has no side-by-side form")
         self._lin(mix, P["wo"], y)
@@ -657,6 +663,14 @@ class RaggedEngine:
         idw = self._idw[:rows]
         ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, self._sel_idx[:rows * e.top].view(rows, e.top),
                       self._sel_w[:rows * e.top].view(rows, e.top), e.experts, e.top)
+        if E == BF and rows <= self.moe_sel_max_rows and ops.moe_sel_supported(s.width, e.ff, e.shared_ff, e.top):
+            # decode rows: stream only the chosen experts' weights (and the shared expert's)
+            n_sel = e.top * e.ff + e.shared_ff
+            ops.moe_sel(he, P["w_gu"], P["w_down"], self._sel_idx[:rows * e.top].view(rows, e.top),
+                        self._sel_w[:rows * e.top].view(rows, e.top), self._act[:rows * n_sel].view(rows, n_sel), y2,
+                        e.experts, e.top, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha)
+            ops.residual_add2(x, y, y2, idw if e.identity else None, hn if e.identity else None)
+            return
         n_gu = P["w_gu"].shape[0]
         gu = self._gu[:rows * n_gu].view(rows, n_gu)
         self._lin(he, P["w_gu"], gu)
@@ -704,11 +718,15 @@ class RaggedEngine:
         qbuf = self._qbuf[:rows * H * (K + R)].view(rows, H * (K + R))
         ops.latent_q_absorb(q, P["uk"], qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, K)
         olat = self._olat[:rows * H * K].view(rows, H * K)
+        # few rows (decode): every row's keys go to several CTAs, so that a long context is read by the whole GPU; the
+        # count depends on the rows alone (a replayed graph keeps it while the contexts grow)
+        splits = max(1, min(16, (4 * self._sms) // (rows * H))) if rows <= 16 else 1
+        part = self._apart if splits > 1 else None
         ops.attn_ragged(qbuf, pool, pool, None, olat, d_rent, d_ent, self.kv.page_table, H, 1, K + R, K, m.scale,
-                        ldv=K + R)
+                        ldv=K + R, splits=splits, part=part)
         ops.latent_v_up(olat, P["uv"], proj if m.out_gate else None, mix, H, V, K, g_off=off["g"])
 
-    def _mamba2(self, li, m, P, proj, mix, rows, views):
+    def _mamba2(self, li, m, P, proj, mix, rows, views, long_step=False):
         d_tok, d_rent, d_ent, d_want, d_tiles = views
         inner, gn = m.heads * m.vdim, m.groups * m.state
         C = inner + 2 * gn
@@ -718,7 +736,7 @@ class RaggedEngine:
                               off["x"], act=1)
         yss = self._oscr[:rows * inner].view(rows, inner)
         ops.ssm_scan_ragged(xbc, proj, self.slots[("S", li)], yss, d_ent, m.heads, m.vdim, m.state, m.groups, off["dt"],
-                            P["dt_bias"], P["a_log"], P["d_skip"])
+                            P["dt_bias"], P["a_log"], P["d_skip"], blocked=long_step)
         ops.gated_group_rmsnorm(yss, proj, P["out_norm"], mix, m.norm_groups, self.spec.eps, off["z"])
 
     # ------------------------------------------------------------------ public API

@@ -443,7 +443,9 @@ int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_st
  * chunk mask (chunk > 0: same block of `chunk` positions) and the window (window > 0) leave, softmax with an optional
  * sink term exp(sink[h]) in the denominator, output turned back by the row's position (cos_v / sin_v) and multiplied
  * by sigmoid(proj[row, g_off + h]) (g_off < 0: no gate) -> out [rows, H, V].  ldv: elements between the value rows of
- * consecutive positions (0 = V); with v_cache == k_cache and ldv = D the values are the first V entries of the keys. */
+ * consecutive positions (0 = V); with v_cache == k_cache and ldv = D the values are the first V entries of the keys.
+ * splits > 1 (few rows over long contexts): the keys of every row are dealt to `splits` CTAs whose partial sums go
+ * through part [rows, H, splits, V + 2] fp32 and a merge kernel. */
 int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_cache, const int32_t* row_ent,
                          const int32_t* ent, const int32_t* page_table, int max_pages, int page_size, int rows, int H,
                          int G, int D, int V, int rd, int ldp, int q_off, int k_off, int v_off, const float* q_norm,
@@ -452,7 +454,8 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
-                    int g_off, const float* cos_v, const float* sin_v, int ldv, int dt, dli_stream_t stream);
+                    int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
+                    dli_stream_t stream);
 
 /* The same attention for steps that hold portions of prompts, on the tensor cores (bf16 caches only): one CTA per
  * 64-row query tile of an entry and query head; tiles[2t] = entry, tiles[2t+1] = first row of the tile within the
@@ -511,14 +514,16 @@ int dli_sigmoid_gate(void* out, const void* proj, int rows, int n, int ldp, int 
  * fp32, tap taps-1 is the current row; bias [C] or NULL; act 1 = SiLU) over columns [off, off + C) of proj, history
  * in tail [slots, taps-1, C] fp32 (advanced) -> out [rows, C] fp32.  dli_ssm_scan_ragged: xbc [rows, H*V + 2*G*N] fp32
  * = x | B | C, dt = softplus(proj[row, dt_off + h] + dt_bias[h]), S [slots, H, N, V] fp32 is read and advanced:
- * S = exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + d_skip[h] x -> y [rows, H*V] fp32.
+ * S = exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + d_skip[h] x -> y [rows, H*V] fp32.  blocked != 0 (steps with
+ * portions of prompts): 64 rows at a time as small fp32 matrix products, where the state and a block fit in shared
+ * memory; 0: token by token (decode steps).  The two agree up to fp32 rounding.
  * dli_gated_group_rmsnorm: out = groupnorm(y * silu(proj[row, z_off : +d])) * w. */
 int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const float* bias, const int32_t* row_ent,
                           const int32_t* ent, float* out, int rows, int n_ent, int C, int taps, int ldp, int off, int act,
                           int dt, dli_stream_t stream);
 int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, const int32_t* ent, int n_ent, int H, int V,
                         int N, int G, int ldp, int dt_off, const float* dt_bias, const float* a_log, const float* d_skip,
-                        int dt, dli_stream_t stream);
+                        int blocked, int dt, dli_stream_t stream);
 int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, void* out, int rows, int d, int groups,
                             float eps, int ldp, int z_off, int dt, dli_stream_t stream);
 
@@ -532,6 +537,14 @@ int dli_moe_route(const float* h, const float* w_router, const float* correction
                   float* sel_w, int rows, int d, int n_out, int n_real, int top, dli_stream_t stream);
 int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp, int ff, float limit, int ff_s,
                 float limit_s, float alpha, int ld, int dt, dli_stream_t stream);
+/* Few rows (decode steps, bf16): only the weights of each row's chosen experts (and the shared expert) are read.
+ * x [rows, d]; w_gu and w_down in the stacked layout of dli_moe_act ([gate; up] per expert, shared last;
+ * w_down [d, n_exp*ff + ff_s]); act_sel [rows, top*ff + ff_s] scratch; y [rows, d] = the weighted sum of the chosen
+ * experts' outputs plus the shared expert's (the pass-through experts' share is added by the caller). */
+int dli_moe_sel_supported(int d, int ff, int ff_s, int top);
+int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const int32_t* sel_idx, const float* sel_w,
+                     void* act_sel, void* y, int rows, int d, int n_exp, int top, int ff, float limit, int ff_s,
+                     float limit_s, float alpha, dli_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -181,3 +181,41 @@ def test_mixture_of_experts(experts, identity, top, shared):
     got = y.double().cpu() + idw.double().cpu()[:, None] * h.double().cpu()
     want = R.moe(h.double().cpu(), Pr, mlp)
     assert (got - want).abs().max() < 1e-4 * want.abs().max()
+
+
+@pytest.mark.parametrize("experts,identity,top,shared", [(4, 2, 2, (16, 0.8)), (3, 0, 1, None), (2, 3, 4, (8, 2.0))])
+def test_chosen_experts_only_path_of_decode_rows(experts, identity, top, shared):
+    """bfloat16 decode rows read only the chosen experts' weights: same result as the path over all experts (both round
+    the projections' outputs to bfloat16) and as the oracle."""
+    from dli_b200 import ops, togalorn
+    from dli_b200.ragged_engine import RaggedEngine
+
+    mlp = moe(experts=experts, identity=identity, top=top, ff=24, limit=0.7, shared=shared)
+    cfg = config([(mamba(), mlp)], width=32, groups=2)
+    spec = togalorn.spec_from_config(cfg)
+    sd = togalorn.random_state_dict(spec, seed=5, std=0.3)
+    eng = RaggedEngine(spec, max_batch=4, max_seq_len=64, page_size=4, dtype=torch.bfloat16)
+    eng.load_tensors(togalorn.model_tensors(spec, sd))
+    P, Pr, e = eng.layers[0], R.sub(sd, "l0.mlp."), spec.layers[0].moe
+    assert ops.moe_sel_supported(32, e.ff, e.shared_ff, e.top)
+    torch.manual_seed(4)
+    rows = 5
+    h = torch.randn(rows, 32, device=DEV)
+    he = h.to(torch.bfloat16)
+    wts, idw = torch.empty(rows, experts, device=DEV), torch.empty(rows, device=DEV)
+    si, sw = torch.empty(rows, top, dtype=torch.int32, device=DEV), torch.empty(rows, top, device=DEV)
+    ops.moe_route(h, P["w_router"], P["corr"], wts, idw, si, sw, experts, top)
+    act_sel = torch.empty(rows, top * e.ff + e.shared_ff, dtype=torch.bfloat16, device=DEV)
+    y = torch.empty(rows, 32, dtype=torch.bfloat16, device=DEV)
+    ops.moe_sel(he, P["w_gu"], P["w_down"], si, sw, act_sel, y, e.experts, e.top, e.ff, e.limit, e.shared_ff, e.shared_limit)
+    gu = torch.empty(rows, P["w_gu"].shape[0], dtype=torch.bfloat16, device=DEV)
+    ops.linear_any(he, P["w_gu"], gu)
+    act = torch.empty(rows, e.total_ff, dtype=torch.bfloat16, device=DEV)
+    ops.moe_act(gu, wts, act, e.experts, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha)
+    y_all = torch.empty(rows, 32, dtype=torch.bfloat16, device=DEV)
+    ops.linear_any(act, P["w_down"], y_all)
+    scale = y_all.float().abs().max()
+    assert (y.float() - y_all.float()).abs().max() <= 0.02 * scale
+    got = y.double().cpu() + idw.double().cpu()[:, None] * he.double().cpu()
+    want = R.moe(he.double().cpu(), Pr, mlp)
+    assert (got - want).abs().max() < 0.03 * want.abs().max()
