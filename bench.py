@@ -702,8 +702,12 @@ def togalorn_kernel_times(eng, spec, T, peaks):
             put(f"{tag}_moe_projections", ms_gu + ms_dn, flops=used)
             res[f"{tag}_moe_projections"]["of_bf16_peak_all_experts"] = round(2 * rows * 3 * W * e.total_ff / ((ms_gu + ms_dn) / 1e3) / tc, 4)
         else:
-            put(f"{tag}_moe_projections", ms_gu + ms_dn, byt=3 * W * (e.top * e.ff + e.shared_ff) * eb)
-            res[f"{tag}_moe_projections"]["of_hbm_all_experts"] = round(3 * W * e.total_ff * eb / ((ms_gu + ms_dn) / 1e3) / hbm, 3)
+            put(f"{tag}_moe_projections_all_experts", ms_gu + ms_dn, byt=3 * W * e.total_ff * eb)
+            if ops.moe_sel_supported(W, e.ff, e.shared_ff, e.top):
+                act_sel = torch.empty(rows, e.top * e.ff + e.shared_ff, dtype=E, device=dev)
+                ms = timeit(lambda: ops.moe_sel(he, P["w_gu"], P["w_down"], si, sw, act_sel, y2, e.experts, e.top, e.ff, e.limit,
+                                                e.shared_ff, e.shared_limit, e.alpha))
+                put(f"{tag}_moe_chosen_experts", ms, byt=3 * W * (e.top * e.ff + e.shared_ff) * eb)
     eng.close_sequence(slot)
     return res
 

@@ -70,6 +70,7 @@ SIGNATURES = {
     "dli_decode_advance": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "dli_embedding_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
     "dli_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "dli_group_rmsnorm_conv_single": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
     "dli_residual_add2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_concat_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_rows_bias_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),

@@ -190,11 +190,22 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
   __syncthreads();
 
   for (int j0 = jb; j0 <= je; j0 += kAttnThreads) {
-    const int j = j0 + tid;
+    // a pass of at most 64 / 32 keys (the key splits of decode rows): 2 / 4 threads share a key's dot product
+    const int cnt_pass = min(kAttnThreads, je - j0 + 1);
+    const int tpk = (a.D % 32 == 0) ? (cnt_pass <= 32 ? 4 : (cnt_pass <= 64 ? 2 : 1)) : 1;
+    const int kidx = tid / tpk, part = tid - kidx * tpk;
+    const int j = j0 + kidx;
     float s = -INFINITY;
-    if (j <= je) {
-      const E* kr = kc + (((size_t)pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size) * a.D;
-      s = dot_row(q, kr, a.D);
+    {
+      float dpart = 0.f;
+      if (j <= je) {
+        const E* kr = kc + (((size_t)pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size) * a.D;
+        const int len = a.D / tpk;
+        dpart = dot_row(q + part * len, kr + part * len, len);
+      }
+      if (tpk > 1) dpart += __shfl_xor_sync(0xffffffffu, dpart, 1);
+      if (tpk > 2) dpart += __shfl_xor_sync(0xffffffffu, dpart, 2);
+      if (j <= je && part == 0) s = dpart;
     }
     // block maximum
     float mx = warp_max(s);
@@ -204,8 +215,8 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     const float m_new = fmaxf(m, mx);
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    const float w = (j <= je) ? expf(s - m_new) : 0.f;
-    p[tid] = w;
+    const float w = (j <= je && part == 0) ? expf(s - m_new) : 0.f;
+    if (part == 0) p[kidx] = w;
     float ws = warp_sum(w);
     if ((tid & 31) == 0) red[4 + (tid >> 5)] = ws;
     __syncthreads();
@@ -215,12 +226,13 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
 #pragma unroll
     for (int i = 0; i < kAttnMaxVPerThread; ++i) acc[i] *= corr;
     if (pv_active) {
-      // four keys per round: their page lookups and value loads are all in flight before the first is used
-      for (int jj = my_group; jj < cnt; jj += 4 * groups) {
-        const E* vr[4];
-        float wj[4];
+      // eight keys per round: their page lookups and value loads are all in flight before the first is used
+      constexpr int KR = 8;
+      for (int jj = my_group; jj < cnt; jj += KR * groups) {
+        const E* vr[KR];
+        float wj[KR];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < KR; ++u) {
           const int ju = jj + u * groups, jk = j0 + min(ju, cnt - 1);
           vr[u] = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.ldv;
           wj[u] = ju < cnt ? p[ju] : 0.f;
@@ -229,11 +241,11 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
         for (int i = 0; i < kAttnMaxVPerThread; ++i) {
           const int d = d0 + i * kAttnThreads;
           if (d < a.V) {
-            float f[4];
+            float f[KR];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) f[u] = a_to_f(vr[u][d]);
+            for (int u = 0; u < KR; ++u) f[u] = a_to_f(vr[u][d]);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc[i] = fmaf(wj[u], f[u], acc[i]);
+            for (int u = 0; u < KR; ++u) acc[i] = fmaf(wj[u], f[u], acc[i]);
           }
         }
       }

@@ -35,11 +35,12 @@ __device__ __forceinline__ float m_block_sum(float v, float* red) {
 
 // out[row, c] = act(bias[c] + sum_j w[c, j] * in[t - taps + 1 + j, c]); in = columns [off, off + C) of proj.
 // Inputs before the entry's first row come from tail [slots, taps-1, C] (oldest first), zeros before position 0.
+// single != 0 (one row per entry): the channel's thread also shifts the slot's tail, so no second kernel is needed.
 template <typename E>
 __global__ void __launch_bounds__(256)
-conv1d_act_kernel(const E* __restrict__ proj, const float* __restrict__ tail, const float* __restrict__ w,
+conv1d_act_kernel(const E* __restrict__ proj, float* __restrict__ tail, const float* __restrict__ w,
                   const float* __restrict__ bias, const int32_t* __restrict__ row_ent, const int32_t* __restrict__ ent,
-                  float* __restrict__ out, int C, int taps, int ldp, int off, int act) {
+                  float* __restrict__ out, int C, int taps, int ldp, int off, int act, int single) {
   pdl_wait();
   pdl_trigger();
   const int row = blockIdx.x;
@@ -57,6 +58,11 @@ conv1d_act_kernel(const E* __restrict__ proj, const float* __restrict__ tail, co
     }
     if (act == 1) acc = acc / (1.f + expf(-acc));
     out[(size_t)row * C + c] = acc;
+    if (single && taps > 1) {  // every old entry was read above; slot i takes old slot i + 1, the last one the current input
+      float* t = tail + (size_t)e.x * (taps - 1) * C + c;
+      for (int i = 0; i + 1 < taps - 1; ++i) t[(size_t)i * C] = (pos - (taps - 2 - i) >= 0) ? t[(size_t)(i + 1) * C] : 0.f;
+      t[(size_t)(taps - 2) * C] = m_to_f(proj[(size_t)row * ldp + off + c]);
+    }
   }
 }
 
@@ -359,9 +365,10 @@ int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const f
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // few rows (decode): the channels of a row are dealt to several CTAs
   const int gy = rows <= 64 ? (C + 255) / 256 : 1, gyt = n_ent <= 64 ? (C + 255) / 256 : 1;
-  if (dt == 0) DLI_LAUNCH("conv1d_act", conv1d_act_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, (const bf16*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
-  else DLI_LAUNCH("conv1d_act", conv1d_act_kernel<float>, dim3(rows, gy), dim3(256), 0, s, (const float*)proj, (const float*)tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act);
-  if (taps > 1) {
+  const int single = rows == n_ent ? 1 : 0;
+  if (dt == 0) DLI_LAUNCH("conv1d_act", conv1d_act_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, (const bf16*)proj, tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act, single);
+  else DLI_LAUNCH("conv1d_act", conv1d_act_kernel<float>, dim3(rows, gy), dim3(256), 0, s, (const float*)proj, tail, w, bias, row_ent, ent, out, C, taps, ldp, off, act, single);
+  if (taps > 1 && !single) {
     if (dt == 0) DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<bf16>, dim3(n_ent, gyt), dim3(256), 0, s, (const bf16*)proj, tail, ent, C, taps, ldp, off);
     else DLI_LAUNCH("conv1d_tail", conv1d_tail_kernel<float>, dim3(n_ent, gyt), dim3(256), 0, s, (const float*)proj, tail, ent, C, taps, ldp, off);
   }
@@ -414,8 +421,9 @@ int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, vo
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("gated_group_rmsnorm", gated_group_rmsnorm_kernel<bf16>, dim3(rows), dim3(256), 0, s, y, (const bf16*)proj, w, (bf16*)out, d, groups, eps, ldp, z_off);
-  else DLI_LAUNCH("gated_group_rmsnorm", gated_group_rmsnorm_kernel<float>, dim3(rows), dim3(256), 0, s, y, (const float*)proj, w, (float*)out, d, groups, eps, ldp, z_off);
+  const int th = (rows <= 64 && d / groups >= 2048) ? 1024 : 256;  // few rows of a wide model: more threads per row
+  if (dt == 0) DLI_LAUNCH("gated_group_rmsnorm", gated_group_rmsnorm_kernel<bf16>, dim3(rows), dim3(th), 0, s, y, (const bf16*)proj, w, (bf16*)out, d, groups, eps, ldp, z_off);
+  else DLI_LAUNCH("gated_group_rmsnorm", gated_group_rmsnorm_kernel<float>, dim3(rows), dim3(th), 0, s, y, (const float*)proj, w, (float*)out, d, groups, eps, ldp, z_off);
   return DLI_OK;
 }
 

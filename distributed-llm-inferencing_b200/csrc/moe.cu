@@ -24,7 +24,7 @@ template <> __device__ __forceinline__ float x_from_f<float>(float v) { return v
 template <> __device__ __forceinline__ bf16 x_from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
 
 // One CTA per row: a warp per router output for the logits, then one warp does the softmax and the choice.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
                  float* __restrict__ wts, float* __restrict__ idw, int32_t* __restrict__ sel_idx,
                  float* __restrict__ sel_w, int d, int n_out, int n_real, int top) {
@@ -38,7 +38,17 @@ moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, cons
   for (int o = warp; o < n_out; o += nw) {
     const float* w = wr + (size_t)o * d;
     float acc = 0.f;
-    for (int c = lane; c < d; c += 32) acc = fmaf(hr[c], w[c], acc);
+    if ((d & 3) == 0) {  // 16-byte loads, four in flight per lane
+      const float4* h4 = reinterpret_cast<const float4*>(hr);
+      const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll 4
+      for (int c = lane; c < d / 4; c += 32) {
+        const float4 a = h4[c], b = w4[c];
+        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+      }
+    } else {
+      for (int c = lane; c < d; c += 32) acc = fmaf(hr[c], w[c], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) zs[o] = acc;
   }
@@ -150,7 +160,7 @@ __device__ __forceinline__ float dot8(const uint4& w, const float* x) {
 }
 
 constexpr int kSelWarps = 8;
-constexpr int kSelPerWarp = 8;  // outputs per warp
+constexpr int kSelPerWarp = 4;  // activation outputs per warp (the down projection: one output per warp)
 
 __global__ void __launch_bounds__(kSelWarps * 32)
 moe_sel_act_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_gu, const int32_t* __restrict__ sel_idx,
@@ -174,22 +184,38 @@ moe_sel_act_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_gu, co
   const float wt = shared ? 1.f : sel_w[row * top + k];
   const float lim = shared ? a.limit_s : a.limit;
   const bf16* base = w_gu + (size_t)e * 2 * a.ff * d;  // the shared expert's block follows the n_exp routed ones
-  for (int f = f0; f < min(f0 + kSelPerWarp, ff); ++f) {
-    const bf16* gr = base + (size_t)f * d;
-    const bf16* ur = base + (size_t)(ff + f) * d;
-    float g = 0.f, u = 0.f;
-    for (int c = lane * 8; c < d; c += 256) {
-      g += dot8(ld_stream_16B(gr + c), xs + c);
-      u += dot8(ld_stream_16B(ur + c), xs + c);
+  for (int f = f0; f < min(f0 + kSelPerWarp, ff); f += 2) {
+    // two outputs at a time: the gate and up rows of both are streamed together (eight 16-byte loads in flight per lane)
+    const int f1 = min(f + 1, ff - 1);
+    const bf16* gr0 = base + (size_t)f * d;
+    const bf16* ur0 = base + (size_t)(ff + f) * d;
+    const bf16* gr1 = base + (size_t)f1 * d;
+    const bf16* ur1 = base + (size_t)(ff + f1) * d;
+    float g0 = 0.f, u0 = 0.f, g1 = 0.f, u1 = 0.f;
+    int c = lane * 8;
+    for (; c + 256 < d; c += 512) {
+      const uint4 a0 = ld_stream_16B(gr0 + c), b0 = ld_stream_16B(ur0 + c), a1 = ld_stream_16B(gr1 + c), b1 = ld_stream_16B(ur1 + c);
+      const uint4 a2 = ld_stream_16B(gr0 + c + 256), b2 = ld_stream_16B(ur0 + c + 256), a3 = ld_stream_16B(gr1 + c + 256),
+                  b3 = ld_stream_16B(ur1 + c + 256);
+      g0 += dot8(a0, xs + c) + dot8(a2, xs + c + 256);
+      u0 += dot8(b0, xs + c) + dot8(b2, xs + c + 256);
+      g1 += dot8(a1, xs + c) + dot8(a3, xs + c + 256);
+      u1 += dot8(b1, xs + c) + dot8(b3, xs + c + 256);
     }
-    g = warp_sum(g);
-    u = warp_sum(u);
-    if (lane == 0) {
+    for (; c < d; c += 256) {
+      g0 += dot8(ld_stream_16B(gr0 + c), xs + c);
+      u0 += dot8(ld_stream_16B(ur0 + c), xs + c);
+      g1 += dot8(ld_stream_16B(gr1 + c), xs + c);
+      u1 += dot8(ld_stream_16B(ur1 + c), xs + c);
+    }
+    g0 = warp_sum(g0); u0 = warp_sum(u0); g1 = warp_sum(g1); u1 = warp_sum(u1);
+    if (lane < 2 && f + lane < ff) {
+      float g = lane ? g1 : g0, u = lane ? u1 : u0;
       g = __bfloat162float(__float2bfloat16_rn(g));  // the projection's output is a bf16 row, as on the dense path
       u = __bfloat162float(__float2bfloat16_rn(u));
       g = fminf(g, lim);
       u = fminf(fmaxf(u, -lim), lim);
-      out[f] = __float2bfloat16_rn(g / (1.f + expf(-a.alpha * g)) * (u + 1.f) * wt);
+      out[f + lane] = __float2bfloat16_rn(g / (1.f + expf(-a.alpha * g)) * (u + 1.f) * wt);
     }
   }
 }
@@ -204,22 +230,34 @@ moe_sel_down_kernel(const bf16* __restrict__ act_sel, const bf16* __restrict__ w
   const int n_sel = top * a.ff + a.ff_s, F = a.n_exp * a.ff + a.ff_s;
   for (int i = threadIdx.x; i < n_sel; i += blockDim.x) as[i] = __bfloat162float(act_sel[(size_t)row * n_sel + i]);
   __syncthreads();
-  const int c0 = (blockIdx.y * kSelWarps + warp) * kSelPerWarp;
-  for (int c = c0; c < min(c0 + kSelPerWarp, d); ++c) {
-    const bf16* wr = w_down + (size_t)c * F;
-    float acc = 0.f;
-    for (int k = 0; k <= top; ++k) {
-      const bool shared = k == top;
-      const int e = shared ? a.n_exp : sel_idx[row * top + k];
-      if (!shared && e >= a.n_exp) continue;
-      const int ff = shared ? a.ff_s : a.ff;
-      const bf16* seg = wr + (size_t)e * a.ff;  // the shared block starts at n_exp * ff
-      const float* av = as + (shared ? top * a.ff : k * a.ff);
-      for (int f = lane * 8; f < ff; f += 256) acc += dot8(ld_stream_16B(seg + f), av + f);
+  const int c = blockIdx.y * kSelWarps + warp;  // one output per warp
+  if (c >= d) return;
+  const bf16* wr = w_down + (size_t)c * F;
+  float acc = 0.f;
+  for (int k = 0; k <= top; ++k) {
+    const bool shared = k == top;
+    const int e = shared ? a.n_exp : sel_idx[row * top + k];
+    if (!shared && e >= a.n_exp) continue;
+    const int ff = shared ? a.ff_s : a.ff;
+    const bf16* seg = wr + (size_t)e * a.ff;  // the shared block starts at n_exp * ff
+    const float* av = as + (shared ? top * a.ff : k * a.ff);
+    int f = lane * 8;
+    for (; f + 7 * 256 < ff; f += 8 * 256) {  // eight 16-byte loads in flight per lane
+      uint4 w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = ld_stream_16B(seg + f + i * 256);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc += dot8(w[i], av + f + i * 256);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) y[(size_t)row * d + c] = __float2bfloat16_rn(acc);
+    for (; f + 3 * 256 < ff; f += 4 * 256) {
+      const uint4 w0 = ld_stream_16B(seg + f), w1 = ld_stream_16B(seg + f + 256), w2 = ld_stream_16B(seg + f + 512),
+                  w3 = ld_stream_16B(seg + f + 768);
+      acc += dot8(w0, av + f) + dot8(w1, av + f + 256) + dot8(w2, av + f + 512) + dot8(w3, av + f + 768);
+    }
+    for (; f < ff; f += 256) acc += dot8(ld_stream_16B(seg + f), av + f);
   }
+  acc = warp_sum(acc);
+  if (lane == 0) y[(size_t)row * d + c] = __float2bfloat16_rn(acc);
 }
 
 }  // namespace dli
@@ -234,7 +272,7 @@ int dli_moe_route(const float* h, const float* w_router, const float* correction
   DLI_CHECK_ARG(d > 0 && n_out > 0 && n_real >= 0 && n_real <= n_out && top > 0 && top <= n_out && n_out <= 4096,
                 "dli_moe_route: %d router outputs (%d real experts), top %d", n_out, n_real, top);
   if (rows <= 0) return DLI_OK;
-  DLI_LAUNCH("moe_route", moe_route_kernel, dim3(rows), dim3(256), (size_t)2 * n_out * sizeof(float),
+  DLI_LAUNCH("moe_route", moe_route_kernel, dim3(rows), dim3(rows <= 64 ? 512 : 256), (size_t)2 * n_out * sizeof(float),
              static_cast<cudaStream_t>(stream), h, w_router, correction, wts, idw, sel_idx, sel_w, d, n_out, n_real, top);
   return DLI_OK;
 }
@@ -274,7 +312,7 @@ int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const 
   const int ffm = ff > ff_s ? ff : ff_s;
   DLI_LAUNCH("moe_sel_act", moe_sel_act_kernel, dim3(rows, top + (ff_s ? 1 : 0), (ffm + per - 1) / per), dim3(kSelWarps * 32),
              (size_t)d * 4, s, (const bf16*)x, (const bf16*)w_gu, sel_idx, sel_w, (bf16*)act_sel, d, top, a);
-  DLI_LAUNCH("moe_sel_down", moe_sel_down_kernel, dim3(rows, (d + per - 1) / per), dim3(kSelWarps * 32),
+  DLI_LAUNCH("moe_sel_down", moe_sel_down_kernel, dim3(rows, (d + kSelWarps - 1) / kSelWarps), dim3(kSelWarps * 32),
              ((size_t)top * ff + ff_s) * 4, s, (const bf16*)act_sel, (const bf16*)w_down, sel_idx, (bf16*)y, d, top, a);
   return DLI_OK;
 }

@@ -74,6 +74,47 @@ group_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, f
   }
 }
 
+// Decode rows (one row per entry): the grouped norm AND the mixer's input convolution with its tail shift in one
+// kernel: hn / he as above, hc = h + conv(h) in the element type (the row's CTA is the only reader and writer of its
+// slot's tail).
+constexpr int kMaxNormGroups = 64;
+template <typename E>
+__global__ void __launch_bounds__(1024)
+group_rmsnorm_conv_single_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ hn,
+                                 E* __restrict__ he, float* __restrict__ tail, const float* __restrict__ cw,
+                                 const int32_t* __restrict__ ent, E* __restrict__ hc, int d, int groups, float eps, int taps) {
+  __shared__ float red[32];
+  __shared__ float rg[kMaxNormGroups];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  const size_t o = (size_t)row * d;
+  const int gd = d / groups;
+  for (int g = 0; g < groups; ++g) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < gd; c += blockDim.x) { const float v = x[o + g * gd + c]; ss += v * v; }
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) rg[g] = 1.f / sqrtf(ss / gd + eps);
+  }
+  __syncthreads();
+  const int4 e = reinterpret_cast<const int4*>(ent)[row];  // slot, row0 (== row), 1, position
+  const int keep = taps - 1;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float cur = x[o + c] * rg[c / gd] * w[c];
+    if (hn) hn[o + c] = cur;
+    if (he) he[o + c] = from_f<E>(cur);
+    float* t = tail + (size_t)e.x * keep * d + c;
+    float acc = cw[(size_t)c * taps + keep] * cur;
+    for (int i = 0; i < keep; ++i) {  // tail slot i holds position pos - keep + i
+      const float v = (e.w - keep + i >= 0) ? t[(size_t)i * d] : 0.f;
+      acc += cw[(size_t)c * taps + i] * v;
+      if (i > 0) t[(size_t)(i - 1) * d] = v;
+    }
+    if (keep > 0) t[(size_t)(keep - 1) * d] = cur;
+    hc[o + c] = from_f<E>(cur + acc);
+  }
+}
+
 // x += y1 + y2 + a[row] * h: the residual add of a layer whose sublayers run side by side on one normed input
 // (y2, and a with h, optional; a[row] is the weight of the branches that pass their input through unchanged).
 template <typename E>
@@ -396,6 +437,23 @@ int dli_group_rmsnorm(const float* x, const float* w, float* hn, void* he, int r
   const int th = (rows <= 64 && d / groups >= 2048) ? 1024 : 256;
   if (dt == 0) DLI_LAUNCH("group_rmsnorm", group_rmsnorm_kernel<bf16>, dim3(rows), dim3(th), 0, s, x, w, hn, (bf16*)he, d, groups, eps);
   else DLI_LAUNCH("group_rmsnorm", group_rmsnorm_kernel<float>, dim3(rows), dim3(th), 0, s, x, w, hn, (float*)he, d, groups, eps);
+  return DLI_OK;
+}
+
+int dli_group_rmsnorm_conv_single(const float* x, const float* w, float* hn, void* he, float* tail, const float* conv_w,
+                                  const int32_t* ent, void* hc, int rows, int d, int groups, float eps, int taps, int dt,
+                                  dli_stream_t stream) {
+  DLI_CHECK_ARG(x && w && conv_w && ent && hc && d > 0 && groups > 0 && groups <= kMaxNormGroups && d % groups == 0 &&
+                    taps >= 1 && (tail || taps == 1),
+                "dli_group_rmsnorm_conv_single: null pointer, or width %d / groups %d (<= %d) / taps %d", d, groups,
+                kMaxNormGroups, taps);
+  DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_group_rmsnorm_conv_single: ent must be 16-byte aligned");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int th = d >= 2048 ? 1024 : 256;
+  if (dt == 0) DLI_LAUNCH("group_rmsnorm_conv_single", group_rmsnorm_conv_single_kernel<bf16>, dim3(rows), dim3(th), 0, s, x, w, hn, (bf16*)he, tail, conv_w, ent, (bf16*)hc, d, groups, eps, taps);
+  else DLI_LAUNCH("group_rmsnorm_conv_single", group_rmsnorm_conv_single_kernel<float>, dim3(rows), dim3(th), 0, s, x, w, hn, (float*)he, tail, conv_w, ent, (float*)hc, d, groups, eps, taps);
   return DLI_OK;
 }
 

@@ -485,6 +485,14 @@ def group_rmsnorm(x, w, groups: int, eps: float, hn=None, he=None):
           _dt(he) if he is not None else 1, _stream())
 
 
+def group_rmsnorm_conv_single(x, w, groups, eps, tail, conv_w, ent, hc, hn=None, he=None):
+    """Decode rows (one per entry): group_rmsnorm (-> hn, he) and causal_conv_ragged of the normed row (-> hc, the slot's
+    tail shifted) as one kernel."""
+    _f32(x, w, hn, tail, conv_w), _i32(ent), _req(hc, hc.dtype), _req(he, hc.dtype)
+    _call("dli_group_rmsnorm_conv_single", 1, _p(x), _p(w), _p(hn), _p(he), _p(tail), _p(conv_w), _p(ent), _p(hc),
+          x.shape[0], x.shape[1], int(groups), float(eps), conv_w.shape[1], _dt(hc), _stream())
+
+
 def residual_add2(x, y1, y2=None, a=None, h=None):
     """x += y1 + y2 + a[:, None] * h (x, a, h float32; y1, y2 in one element type)."""
     _f32(x, a, h), _req(y1, y1.dtype), _req(y2, y1.dtype)
@@ -689,7 +697,7 @@ def conv1d_act_ragged(proj, tail, w, bias, row_ent, ent, out, off, act=1):
     slots' histories tail float32 [slots, taps-1, C] are advanced."""
     _req(proj, proj.dtype), _f32(tail, w, bias, out), _i32(row_ent, ent)
     C, taps = w.shape
-    _call("dli_conv1d_act_ragged", 2 if taps > 1 else 1, _p(proj), _p(tail), _p(w), _p(bias), _p(row_ent), _p(ent), _p(out),
+    _call("dli_conv1d_act_ragged", 2 if (taps > 1 and proj.shape[0] != ent.numel() // 4) else 1, _p(proj), _p(tail), _p(w), _p(bias), _p(row_ent), _p(ent), _p(out),
           proj.shape[0], ent.numel() // 4, C, taps, proj.shape[1], off, int(act), _dt(proj), _stream())
     return out
 

@@ -639,8 +639,14 @@ class RaggedEngine:
         d_tok, d_rent, d_ent, d_want, d_tiles = views
         x, hn, hc, he, y = self._x[:rows], self._hn[:rows], self._hc[:rows], self._he[:rows], self._y[:rows]
         has_ff = L.moe is not None
-        ops.group_rmsnorm(x, P["norm1"], s.norm_groups, s.eps, hn=hn, he=he if has_ff else None)
-        ops.causal_conv_ragged(hn, self.slots.tensors.get(("tail1", li)), P["canon1"], d_rent, d_ent, hc)
+        need_hn = has_ff  # the router and the pass-through experts read the normed row in fp32
+        if rows == n_ent and s.taps > 1 and s.norm_groups <= 64:
+            # decode rows: norm, input convolution and tail shift in one kernel
+            ops.group_rmsnorm_conv_single(x, P["norm1"], s.norm_groups, s.eps, self.slots[("tail1", li)], P["canon1"], d_ent,
+                                          hc, hn=hn if need_hn else None, he=he if has_ff else None)
+        else:
+            ops.group_rmsnorm(x, P["norm1"], s.norm_groups, s.eps, hn=hn, he=he if has_ff else None)
+            ops.causal_conv_ragged(hn, self.slots.tensors.get(("tail1", li)), P["canon1"], d_rent, d_ent, hc)
         m = L.mixer
         n_proj = P["w_proj"].shape[0]
         proj = self._proj[:rows * n_proj].view(rows, n_proj)
@@ -720,7 +726,7 @@ class RaggedEngine:
         olat = self._olat[:rows * H * K].view(rows, H * K)
         # few rows (decode): every row's keys go to several CTAs, so that a long context is read by the whole GPU; the
         # count depends on the rows alone (a replayed graph keeps it while the contexts grow)
-        splits = max(1, min(16, (4 * self._sms) // (rows * H))) if rows <= 16 else 1
+        splits = max(1, min(32, (8 * self._sms) // (rows * H))) if rows <= 16 else 1
         part = self._apart if splits > 1 else None
         ops.attn_ragged(qbuf, pool, pool, None, olat, d_rent, d_ent, self.kv.page_table, H, 1, K + R, K, m.scale,
                         ldv=K + R, splits=splits, part=part)

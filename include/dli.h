@@ -408,6 +408,11 @@ int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2
  * hn (fp32) and he (element type dt) are optional outputs. */
 int dli_group_rmsnorm(const float* x, const float* w, float* hn, void* he, int rows, int d, int groups, float eps, int dt,
                       dli_stream_t stream);
+/* Steps of one row per entry (decode): dli_group_rmsnorm and dli_causal_conv_ragged of the normed row (hc = h +
+ * conv(h), the slot's tail shifted) as one kernel; groups <= 64. */
+int dli_group_rmsnorm_conv_single(const float* x, const float* w, float* hn, void* he, float* tail, const float* conv_w,
+                                  const int32_t* ent, void* hc, int rows, int d, int groups, float eps, int taps, int dt,
+                                  dli_stream_t stream);
 /* x += y1 + y2 + a[row] * h (y2, and a with h, optional): residual add of sublayers that run side by side. */
 int dli_residual_add2(float* x, const void* y1, const void* y2, const float* a, const float* h, int rows, int d, int dt,
                       dli_stream_t stream);
