@@ -675,7 +675,13 @@ def togalorn_kernel_times(eng, spec, T, peaks):
                     n=3, reps=3)
         if rows > 1:
             # FMAs counted as 2: per 64-row block and head C.B^T (64*64*N), G.x (64*64*V), C.S and the state update (2*64*N*V)
-            put(f"{tag}_ssm_scan_blocked", ms, fp32=2 * rows * m.heads * (64 * m.state + 64 * m.vdim + 2 * m.state * m.vdim))
+            bl_flops = 2 * rows * m.heads * (64 * m.state + 64 * m.vdim + 2 * m.state * m.vdim)
+            put(f"{tag}_ssm_scan_blocks_in_order", ms, fp32=bl_flops)
+            scr = torch.empty(ops.ssm_parallel_scratch_floats(tiles.shape[0], m.heads, m.state, m.vdim), device=dev)
+            ms = timeit(lambda: ops.ssm_scan_ragged(xbc, proj, eng.slots[("S", li_s)], yss, ent, m.heads, m.vdim, m.state,
+                                                    m.groups, off["dt"], P["dt_bias"], P["a_log"], P["d_skip"], blocked=True,
+                                                    tiles=tiles, scratch=scr), n=3, reps=3)
+            put(f"{tag}_ssm_scan_blocks_parallel", ms, fp32=bl_flops)
             ms = timeit(lambda: ops.ssm_scan_ragged(xbc, proj, eng.slots[("S", li_s)], yss, ent, m.heads, m.vdim, m.state,
                                                     m.groups, off["dt"], P["dt_bias"], P["a_log"], P["d_skip"]), n=2, reps=1)
             put(f"{tag}_ssm_scan_token_by_token", ms, fp32=rows * m.heads * m.state * m.vdim * 5)

@@ -81,7 +81,8 @@ SIGNATURES = {
     "dli_latent_expand": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_sigmoid_gate": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "dli_conv1d_act_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
-    "dli_ssm_scan_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "dli_ssm_scan_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp]),
+    "dli_ssm_parallel_scratch_floats": (_sz, [_i, _i, _i, _i]),
     "dli_gated_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _vp]),
     "dli_moe_route": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "dli_moe_sel_supported": (_i, [_i, _i, _i, _i]),

@@ -168,10 +168,17 @@ static inline size_t ssm_blocked_smem_bytes(int N, int V) {
   return sizeof(float) * ((size_t)2 * kSsmL * (N + 1) + (size_t)kSsmL * V + (size_t)N * V + (size_t)kSsmL * (kSsmL + 1) + 3 * kSsmL);
 }
 
-template <typename E>
+//
+// When an entry spans several blocks they run in parallel (mode 1, carry, mode 3): every block first computes what it
+// adds to the state as if it started from nothing (U_c = sum_s e^(c_L - c_s) dt_s B_s x_s^T, and its decay e^(c_L)),
+// an elementwise pass carries the state over the blocks in order (S <- e^(c_L) S + U_c, leaving each block's
+// incoming state where U_c was), then all blocks compute their outputs from their incoming states.
+//   mode 0: one CTA per (entry, head) walks the blocks in order;  mode 1 / 3: one CTA per (block, head).
+template <typename E, int mode>
 __global__ void __launch_bounds__(256)
 ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ proj, float* __restrict__ S,
-                        float* __restrict__ y, SsmRun a) {
+                        float* __restrict__ y, SsmRun a, const int32_t* __restrict__ tiles,
+                        float* __restrict__ scr_u, float* __restrict__ scr_decay) {
   extern __shared__ float sm[];
   const int N = a.N, V = a.V, NP = N + 1, LP = kSsmL + 1;
   float* Bs = sm;                       // [L][N+1]
@@ -184,14 +191,20 @@ ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ pro
   float* wl = dts + kSsmL;              // [L] exp(c_L - c_s) dt_s
   pdl_wait();
   pdl_trigger();
-  const int4 e = reinterpret_cast<const int4*>(a.ent)[blockIdx.x];  // slot, row0, n, start
+  const int ei = mode == 0 ? (int)blockIdx.x : tiles[2 * blockIdx.x];
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[ei];  // slot, row0, n, start
   const int h = blockIdx.y, g = h / (a.H / a.G), tid = threadIdx.x;
   const int tr = tid >> 4, tc = tid & 15;
   const int inner = a.H * V;
   float* Sp = S + (((size_t)e.x * a.H + h) * N) * V;
-  for (int i = tid; i < N * V; i += 256) St[i] = e.w > 0 ? Sp[i] : 0.f;
+  float* Up = mode == 0 ? nullptr : scr_u + ((size_t)blockIdx.x * a.H + h) * N * V;
+  if (mode == 0) for (int i = tid; i < N * V; i += 256) St[i] = e.w > 0 ? Sp[i] : 0.f;
+  if (mode == 1) for (int i = tid; i < N * V; i += 256) St[i] = 0.f;
+  if (mode == 3) for (int i = tid; i < N * V; i += 256) St[i] = Up[i];
   const float na = -expf(a.a_log[h]), db = a.dt_bias[h], dk = a.d_skip[h];
-  for (int b0 = 0; b0 < e.z; b0 += kSsmL) {
+  const int b_first = mode == 0 ? 0 : tiles[2 * blockIdx.x + 1];
+  const int b_end = mode == 0 ? e.z : min(e.z, b_first + kSsmL);
+  for (int b0 = b_first; b0 < b_end; b0 += kSsmL) {
     const int nb = min(kSsmL, e.z - b0);
     __syncthreads();  // the previous block's reads of Bs, Cs, Xs, Gs are done; St is complete
     for (int i = tid; i < kSsmL * N; i += 256) {
@@ -221,7 +234,7 @@ ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ pro
     __syncthreads();
     if (tid < kSsmL) wl[tid] = expf(cum[kSsmL - 1] - cum[tid]) * dts[tid];
     // G[t][s] = (C_t . B_s) exp(c_t - c_s) dt_s for s <= t
-    {
+    if (mode != 1) {
       float acc[4][4] = {};
       for (int k = 0; k < N; ++k) {
         float cv[4], bv[4];
@@ -244,7 +257,7 @@ ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ pro
     }
     __syncthreads();
     // y[t][v] = sum_s G[t][s] x[s][v] + exp(c_t) sum_n C[t][n] S[n][v] + D x[t][v]
-    for (int v0 = 0; v0 < V; v0 += 64) {
+    for (int v0 = 0; v0 < V && mode != 1; v0 += 64) {
       float acc[4][4] = {}, acs[4][4] = {};
       int vv[4];
 #pragma unroll
@@ -284,8 +297,10 @@ ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ pro
       }
     }
     __syncthreads();  // every read of the incoming state is done
+    if (mode == 3) break;
     // S[n][v] = exp(c_L) S[n][v] + sum_s wl[s] B[s][n] x[s][v]
     const float eL = expf(cum[kSsmL - 1]);
+    if (mode == 1 && tid == 0) scr_decay[(size_t)blockIdx.x * a.H + h] = eL;
     for (int n0 = 0; n0 < N; n0 += 64)
       for (int v0 = 0; v0 < V; v0 += 64) {
         float acc[4][4] = {};
@@ -316,7 +331,46 @@ ssm_scan_blocked_kernel(const float* __restrict__ xbc, const E* __restrict__ pro
       }
   }
   __syncthreads();
-  for (int i = tid; i < N * V; i += 256) Sp[i] = St[i];
+  if (mode == 0) for (int i = tid; i < N * V; i += 256) Sp[i] = St[i];
+  if (mode == 1) for (int i = tid; i < N * V; i += 256) Up[i] = St[i];
+}
+
+// The carry over an entry's blocks in order, elementwise: grid (entries, heads, ceil(N*V / 256)).
+__global__ void __launch_bounds__(256)
+ssm_par_carry_kernel(const int32_t* __restrict__ ent, const int32_t* __restrict__ tiles, int n_tiles, float* __restrict__ S,
+                     float* __restrict__ scr_u, const float* __restrict__ scr_decay, int H, int NV) {
+  __shared__ int t_first;
+  pdl_wait();
+  pdl_trigger();
+  const int4 e = reinterpret_cast<const int4*>(ent)[blockIdx.x];
+  const int h = blockIdx.y;
+  if (threadIdx.x == 0) {
+    int t = 0;
+    while (t < n_tiles && tiles[2 * t] != (int)blockIdx.x) ++t;
+    t_first = t;
+  }
+  __syncthreads();
+  const int i = blockIdx.z * 256 + threadIdx.x;
+  if (i >= NV) return;
+  const int nt = (e.z + kSsmL - 1) / kSsmL;
+  float* Sp = S + ((size_t)e.x * H + h) * NV + i;
+  float s = e.w > 0 ? *Sp : 0.f;
+  for (int c0 = 0; c0 < nt; c0 += 4) {  // four blocks' contributions requested before the first is used
+    float u[4], dcy[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const size_t t = (size_t)t_first + min(c0 + k, nt - 1);
+      u[k] = scr_u[(t * H + h) * NV + i];
+      dcy[k] = scr_decay[t * H + h];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (c0 + k >= nt) break;
+      scr_u[(((size_t)t_first + c0 + k) * H + h) * NV + i] = s;
+      s = fmaf(dcy[k], s, u[k]);
+    }
+  }
+  *Sp = s;
 }
 
 // out[row] = groupnorm(y[row] * silu(z[row])) * w; z = columns [z_off, z_off + d) of proj.
@@ -377,7 +431,7 @@ int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const f
 
 int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, const int32_t* ent, int n_ent, int H, int V,
                         int N, int G, int ldp, int dt_off, const float* dt_bias, const float* a_log, const float* d_skip,
-                        int blocked, int dt, dli_stream_t stream) {
+                        int blocked, const int32_t* tiles, int n_tiles, float* scratch, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(xbc && proj && S && y && ent && dt_bias && a_log && d_skip, "dli_ssm_scan_ragged: null pointer");
   DLI_CHECK_ARG(H > 0 && V > 0 && N > 0 && G > 0 && H % G == 0 && N <= 32 * kSsmMaxPerThread,
                 "dli_ssm_scan_ragged: H=%d V=%d N=%d G=%d (H %% G == 0, N <= %d)", H, V, N, G, 32 * kSsmMaxPerThread);
@@ -388,14 +442,30 @@ int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, 
   if (blocked && bsmem <= 200 * 1024) {
     SsmRun b{ent, H, V, N, G, H * V + 2 * G * N, ldp, dt_off, dt_bias, a_log, d_skip, 0, 0};
     cudaStream_t bs = static_cast<cudaStream_t>(stream);
-    static PerDeviceOnce once_b, once_f;
-    if (dt == 0) {
-      DLI_ONCE_PER_DEVICE(once_b, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(ssm_scan_blocked_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
-      DLI_LAUNCH("ssm_scan_blocked", ssm_scan_blocked_kernel<bf16>, dim3(n_ent, H), dim3(256), bsmem, bs, xbc, (const bf16*)proj, S, y, b);
-    } else {
-      DLI_ONCE_PER_DEVICE(once_f, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(ssm_scan_blocked_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
-      DLI_LAUNCH("ssm_scan_blocked", ssm_scan_blocked_kernel<float>, dim3(n_ent, H), dim3(256), bsmem, bs, xbc, (const float*)proj, S, y, b);
+    // some entry spans several blocks and the caller gave scratch: all blocks in parallel (local, carry, outputs)
+    const bool par = tiles && scratch && n_tiles > n_ent;
+    float* scr_u = scratch;
+    float* scr_d = par ? scratch + (size_t)n_tiles * H * N * V : nullptr;
+#define SSM_BLOCKED_LAUNCH(T, MODE, GRID, WHAT)                                                                              \
+  do {                                                                                                                      \
+    static PerDeviceOnce once;                                                                                              \
+    DLI_ONCE_PER_DEVICE(once, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(ssm_scan_blocked_kernel<T, MODE>,                     \
+                                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024))); \
+    DLI_LAUNCH(WHAT, (ssm_scan_blocked_kernel<T, MODE>), GRID, dim3(256), bsmem, bs, xbc, (const T*)proj, S, y, b, tiles, scr_u, \
+               scr_d);                                                                                                      \
+  } while (0)
+    if (!par) {
+      if (dt == 0) SSM_BLOCKED_LAUNCH(bf16, 0, dim3(n_ent, H), "ssm_scan_blocked");
+      else SSM_BLOCKED_LAUNCH(float, 0, dim3(n_ent, H), "ssm_scan_blocked");
+      return DLI_OK;
     }
+    if (dt == 0) SSM_BLOCKED_LAUNCH(bf16, 1, dim3(n_tiles, H), "ssm_par_local");
+    else SSM_BLOCKED_LAUNCH(float, 1, dim3(n_tiles, H), "ssm_par_local");
+    DLI_LAUNCH("ssm_par_carry", ssm_par_carry_kernel, dim3(n_ent, H, (N * V + 255) / 256), dim3(256), 0, bs, ent, tiles, n_tiles,
+               S, scr_u, (const float*)scr_d, H, N * V);
+    if (dt == 0) SSM_BLOCKED_LAUNCH(bf16, 3, dim3(n_tiles, H), "ssm_par_out");
+    else SSM_BLOCKED_LAUNCH(float, 3, dim3(n_tiles, H), "ssm_par_out");
+#undef SSM_BLOCKED_LAUNCH
     return DLI_OK;
   }
   int np = 1;
@@ -412,6 +482,10 @@ int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, 
   if (dt == 0) DLI_LAUNCH("ssm_scan", ssm_scan_kernel<bf16>, grid, dim3(threads), 0, s, xbc, (const bf16*)proj, S, y, a);
   else DLI_LAUNCH("ssm_scan", ssm_scan_kernel<float>, grid, dim3(threads), 0, s, xbc, (const float*)proj, S, y, a);
   return DLI_OK;
+}
+
+size_t dli_ssm_parallel_scratch_floats(int n_tiles, int H, int N, int V) {
+  return (size_t)n_tiles * H * ((size_t)N * V + 1);
 }
 
 int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, void* out, int rows, int d, int groups,

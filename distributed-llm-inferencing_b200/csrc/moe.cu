@@ -193,6 +193,7 @@ moe_sel_act_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_gu, co
     const bf16* ur1 = base + (size_t)(ff + f1) * d;
     float g0 = 0.f, u0 = 0.f, g1 = 0.f, u1 = 0.f;
     int c = lane * 8;
+#pragma unroll 2
     for (; c + 256 < d; c += 512) {
       const uint4 a0 = ld_stream_16B(gr0 + c), b0 = ld_stream_16B(ur0 + c), a1 = ld_stream_16B(gr1 + c), b1 = ld_stream_16B(ur1 + c);
       const uint4 a2 = ld_stream_16B(gr0 + c + 256), b2 = ld_stream_16B(ur0 + c + 256), a3 = ld_stream_16B(gr1 + c + 256),

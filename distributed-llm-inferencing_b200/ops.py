@@ -702,12 +702,25 @@ def conv1d_act_ragged(proj, tail, w, bias, row_ent, ent, out, off, act=1):
     return out
 
 
-def ssm_scan_ragged(xbc, proj, S, y, ent, H, V, N, G, dt_off, dt_bias, a_log, d_skip, blocked=False):
+def ssm_parallel_scratch_floats(n_tiles, H, N, V) -> int:
+    return int(_lib.load().dli_ssm_parallel_scratch_floats(int(n_tiles), int(H), int(N), int(V)))
+
+
+def ssm_scan_ragged(xbc, proj, S, y, ent, H, V, N, G, dt_off, dt_bias, a_log, d_skip, blocked=False, tiles=None,
+                    scratch=None):
     """The state-space recurrence over the rows of every entry; S float32 [slots, H, N, V] is advanced; y float32
-    [rows, H*V].  blocked: 64 rows at a time (steps with portions of prompts)."""
-    _f32(xbc, S, y, dt_bias, a_log, d_skip), _req(proj, proj.dtype), _i32(ent)
-    _call("dli_ssm_scan_ragged", 1, _p(xbc), _p(proj), _p(S), _p(y), _p(ent), ent.numel() // 4, H, V, N, G, proj.shape[1],
-          dt_off, _p(dt_bias), _p(a_log), _p(d_skip), int(bool(blocked)), _dt(proj), _stream())
+    [rows, H*V].  blocked: 64 rows at a time (steps with portions of prompts); with tiles int32 [n_tiles, 2] = (entry,
+    first row of the block within the entry) and scratch of ssm_parallel_scratch_floats(...) floats the blocks of an
+    entry run in parallel."""
+    _f32(xbc, S, y, dt_bias, a_log, d_skip, scratch), _req(proj, proj.dtype), _i32(ent, tiles)
+    n_ent = ent.numel() // 4
+    n_tiles = tiles.numel() // 2 if tiles is not None else 0
+    par = bool(blocked) and tiles is not None and scratch is not None and n_tiles > n_ent
+    if par and scratch.numel() < ssm_parallel_scratch_floats(n_tiles, H, N, V):
+        raise ValueError("ssm_scan_ragged: scratch too small")
+    _call("dli_ssm_scan_ragged", 3 if par else 1, _p(xbc), _p(proj), _p(S), _p(y), _p(ent), n_ent, H, V, N, G, proj.shape[1],
+          dt_off, _p(dt_bias), _p(a_log), _p(d_skip), int(bool(blocked)), _p(tiles) if par else None, n_tiles if par else 0,
+          _p(scratch) if par else None, _dt(proj), _stream())
     return y
 
 

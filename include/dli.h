@@ -521,14 +521,18 @@ int dli_sigmoid_gate(void* out, const void* proj, int rows, int n, int ldp, int 
  * = x | B | C, dt = softplus(proj[row, dt_off + h] + dt_bias[h]), S [slots, H, N, V] fp32 is read and advanced:
  * S = exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + d_skip[h] x -> y [rows, H*V] fp32.  blocked != 0 (steps with
  * portions of prompts): 64 rows at a time as small fp32 matrix products, where the state and a block fit in shared
- * memory; 0: token by token (decode steps).  The two agree up to fp32 rounding.
+ * memory; 0: token by token (decode steps).  With tiles (as for dli_attn_ragged_tc: every entry's 64-row blocks,
+ * consecutive per entry) and scratch of dli_ssm_parallel_scratch_floats(...) floats, an entry that spans several blocks
+ * has them run in parallel (local state contributions, an elementwise carry in order, outputs).  All forms agree up to
+ * fp32 rounding.
  * dli_gated_group_rmsnorm: out = groupnorm(y * silu(proj[row, z_off : +d])) * w. */
 int dli_conv1d_act_ragged(const void* proj, float* tail, const float* w, const float* bias, const int32_t* row_ent,
                           const int32_t* ent, float* out, int rows, int n_ent, int C, int taps, int ldp, int off, int act,
                           int dt, dli_stream_t stream);
 int dli_ssm_scan_ragged(const float* xbc, const void* proj, float* S, float* y, const int32_t* ent, int n_ent, int H, int V,
                         int N, int G, int ldp, int dt_off, const float* dt_bias, const float* a_log, const float* d_skip,
-                        int blocked, int dt, dli_stream_t stream);
+                        int blocked, const int32_t* tiles, int n_tiles, float* scratch, int dt, dli_stream_t stream);
+size_t dli_ssm_parallel_scratch_floats(int n_tiles, int H, int N, int V);
 int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, void* out, int rows, int d, int groups,
                             float eps, int ldp, int z_off, int dt, dli_stream_t stream);
 

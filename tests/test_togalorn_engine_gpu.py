@@ -307,3 +307,22 @@ def test_bfloat16_portions_of_latent_attention_on_the_tensor_cores():
     eng.step([(a, toks[:50])])
     both = eng.step([(a, [toks[50]]), (b, toks[:90])], [[0], list(range(90))]).float().cpu()
     assert close16(rel_err(both[:1], ref[50:51])) and close16(rel_err(both[1:], ref[:90]))
+
+
+def test_bfloat16_decode_rows_of_a_sparse_mixture_read_only_the_chosen_experts():
+    """8 experts, 2 per token, no shared expert: decode steps take the kernel that streams the chosen experts' weights
+    only, portions of prompts the GEMMs over all experts; both against the oracle and against each other."""
+    cfg = config([(mamba(), moe(experts=8, identity=1, top=2, ff=24, shared=None)),
+                  (latent(), moe(experts=8, identity=0, top=1, ff=16, shared=(8, 1.0)))], width=64)
+    eng, sd = build(cfg, torch.bfloat16)
+    e = eng.spec.layers[0].moe
+    assert eng.moe_sel_share * (e.top * e.ff + e.shared_ff) <= e.total_ff
+    toks = prompt(40, cfg["vocab"], 8)
+    ref, _ = R.forward(cfg, sd, toks)
+    whole = run_schedule(eng, toks, [40])
+    single = run_schedule(eng, toks, [20])        # 20 decode steps
+    eng.moe_sel_max_rows = 0
+    dense = run_schedule(eng, toks, [20])
+    for got in (whole, single, dense):
+        assert close16(rel_err(got, ref))
+    assert close16(rel_err(single, dense.double()))

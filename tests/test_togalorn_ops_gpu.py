@@ -36,6 +36,12 @@ def step_views(eng, entries):
     return (z, torch.tensor(row_ent, dtype=torch.int32, device=DEV), torch.tensor(ent, dtype=torch.int32, device=DEV), z, z), r
 
 
+def tiles_of(entries):
+    """(entry, first row of every 64-row block within the entry), as a step builds them."""
+    t = [[i, q0] for i, (_, n, _) in enumerate(entries) for q0 in range(0, n, 64)]
+    return torch.tensor(t, dtype=torch.int32, device=DEV)
+
+
 def run_mixer(eng, kind, u, cuts, slot_order=(2,)):
     """u [T, n_proj]: the mixer's input projection (made on the host), fed through the engine's mixer kernels in
     portions of the given sizes (then token by token) -> the mixer's output before its out-projection [T, H*V]."""
@@ -53,13 +59,14 @@ def run_mixer(eng, kind, u, cuts, slot_order=(2,)):
             eng.kv.reserve(slot, at + n)
             eng.kv.commit()
         views, rows = step_views(eng, [(slot, n, at)])
+        views = views[:4] + (tiles_of([(slot, n, at)]),)
         proj = torch.zeros(n, n_proj, device=DEV)
         proj[:, :u.shape[1]] = u[at:at + n].float().to(DEV)
         mix = torch.empty(n, m.heads * m.vdim, device=DEV)
         if kind == "latent_attention":
             eng._latent_attention(0, m, P, proj, mix, n, views)
         else:
-            eng._mamba2(0, m, P, proj, mix, n, views)
+            eng._mamba2(0, m, P, proj, mix, n, views, long_step=n >= 16)   # portions: block-wise, in parallel from 65 rows
         outs.append(mix.double().cpu())
         at += n
     return torch.cat(outs)
@@ -119,7 +126,7 @@ def test_latent_attention_sharp_scores_over_hundreds_of_keys(cuts):
     assert (R.latent_attention(h, P, m2, 1e-5) - want).abs().max() > 0.05 * want.abs().max()
 
 
-@pytest.mark.parametrize("cuts", [[120], [1, 2, 3, 50], [64, 2]])
+@pytest.mark.parametrize("cuts", [[120], [1, 2, 3, 50], [64, 2], [5, 115]])
 def test_state_space_mixer_with_slow_forgetting(cuts):
     """A_log very negative: the state forgets over hundreds of tokens, so the last outputs carry the first inputs; the
     slot holds garbage before (state and convolution history)."""
