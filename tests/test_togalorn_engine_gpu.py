@@ -71,6 +71,19 @@ def cfg_c():
                   width=20, vocab=19, taps=1, groups=5, loop=(0, 2, 3))
 
 
+def cfg_d():
+    """state-space layers only (no paged cache at all), the last two looped; one without feed-forward."""
+    return config([(mamba(), moe(top=1)), (mamba(heads=3, vdim=8, state=6, groups=3, norm_groups=4, conv=2), None),
+                   (mamba(heads=2, vdim=12, state=5, groups=1, norm_groups=1, conv=3), moe(identity=0))], width=32, groups=2,
+                  loop=(1, 3, 2))
+
+
+def cfg_e():
+    """latent-attention layers only, the first one looped three times by itself."""
+    return config([(latent(), moe()), (latent(heads=1, dim=16, rot_dim=2, vdim=4, kv_rank=6, q_rank=10, scale=0.3), None)],
+                  width=32, groups=8, loop=(0, 1, 3), taps=4)
+
+
 def build(cfg, dtype, seed=0, max_batch=4, max_seq_len=256, pool=None, page_size=4):
     from dli_b200 import togalorn
     from dli_b200.ragged_engine import RaggedEngine
@@ -119,7 +132,7 @@ def close16(err):
     return bool((err < TOL16).double().mean() >= 0.97 and err.max() < 0.5)
 
 
-@pytest.mark.parametrize("make", [cfg_a, cfg_b, cfg_c])
+@pytest.mark.parametrize("make", [cfg_a, cfg_b, cfg_c, cfg_d, cfg_e])
 def test_whole_prompt_float32_matches_oracle_at_every_position(make):
     cfg = make()
     eng, sd = build(cfg, torch.float32)
@@ -141,7 +154,7 @@ def test_residual_stream_after_every_layer_run(make):
         assert (got.double().cpu() - ref).abs().max() < 1e-4 * ref.abs().max()
 
 
-@pytest.mark.parametrize("make", [cfg_a, cfg_b, cfg_c])
+@pytest.mark.parametrize("make", [cfg_a, cfg_b, cfg_c, cfg_d, cfg_e])
 @pytest.mark.parametrize("cuts", [[], [1, 1, 2], [2, 2, 3, 5, 7, 11], [17, 2, 16, 3], [30]])
 def test_portions_and_decoding_float32(make, cuts):
     """Token by token from the first token; portions of 2..; a prompt then decoding over page borders."""
