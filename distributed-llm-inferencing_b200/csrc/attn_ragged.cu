@@ -147,7 +147,25 @@ __device__ __forceinline__ float dot_row(const float* q, const float* kr, int D)
   return d;
 }
 
+// four consecutive values of a row as one load (8 bytes of bf16, 16 of float)
+__device__ __forceinline__ void load4(const bf16* p, float* f) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
+}
+__device__ __forceinline__ void load4(const float* p, float* f) {
+  const float4 u = *reinterpret_cast<const float4*>(p);
+  f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+}
+
 constexpr int kAttnThreads = 128;
+// The weighted value sum deals the value dimensions to threads in one of two ways.  Vector form (value size and row stride
+// multiples of 4): a thread owns 4 CONSECUTIVE dimensions and reads them with one load per key; V/4 threads cover a row and
+// 128 / (V/4) key groups work side by side.  Scalar form (any even V): a thread owns dimensions d0, d0 + 128, ...
+__host__ __device__ inline bool attn_vec_values(int V, int ldv) { return V % 4 == 0 && ldv % 4 == 0 && kAttnThreads % (V / 4) == 0; }
+__host__ __device__ inline int attn_value_groups(int V, int ldv) {
+  if (attn_vec_values(V, ldv)) return kAttnThreads / (V / 4);
+  return V >= kAttnThreads ? 1 : kAttnThreads / V;
+}
 constexpr int kAttnMaxVPerThread = 4;  // V <= 512
 
 // One CTA per (row, query head).  Keys in tiles of 128: one score per thread, a block-wide running maximum,
@@ -179,10 +197,12 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     je = min(pos, jb + per - 1);
   }
 
-  const int groups = a.V >= kAttnThreads ? 1 : kAttnThreads / a.V;
-  const int my_group = a.V >= kAttnThreads ? 0 : tid / a.V;
+  const bool vec = attn_vec_values(a.V, a.ldv);
+  const int groups = attn_value_groups(a.V, a.ldv);
+  const int my_group = vec ? tid / (a.V / 4) : (a.V >= kAttnThreads ? 0 : tid / a.V);
   const bool pv_active = my_group < groups;
-  const int d0 = a.V >= kAttnThreads ? tid : tid % a.V;
+  const int d0 = vec ? (tid % (a.V / 4)) * 4 : (a.V >= kAttnThreads ? tid : tid % a.V);
+  const int dstep = vec ? 1 : kAttnThreads;  // acc[i] belongs to dimension d0 + i * dstep
   float acc[kAttnMaxVPerThread] = {0.f, 0.f, 0.f, 0.f};
   const bool has_sink = a.sink && blockIdx.z == 0;
   float m = has_sink ? a.sink[h] : -INFINITY;  // the sink enters as a term exp(sink - m) = 1 of the denominator
@@ -237,15 +257,25 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
           vr[u] = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.ldv;
           wj[u] = ju < cnt ? p[ju] : 0.f;
         }
+        if (vec) {
+          float f[KR][4];
 #pragma unroll
-        for (int i = 0; i < kAttnMaxVPerThread; ++i) {
-          const int d = d0 + i * kAttnThreads;
-          if (d < a.V) {
-            float f[KR];
+          for (int u = 0; u < KR; ++u) load4(vr[u] + d0, f[u]);
 #pragma unroll
-            for (int u = 0; u < KR; ++u) f[u] = a_to_f(vr[u][d]);
+          for (int u = 0; u < KR; ++u)
 #pragma unroll
-            for (int u = 0; u < KR; ++u) acc[i] = fmaf(wj[u], f[u], acc[i]);
+            for (int i = 0; i < 4; ++i) acc[i] = fmaf(wj[u], f[u][i], acc[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < kAttnMaxVPerThread; ++i) {
+            const int d = d0 + i * kAttnThreads;
+            if (d < a.V) {
+              float f[KR];
+#pragma unroll
+              for (int u = 0; u < KR; ++u) f[u] = a_to_f(vr[u][d]);
+#pragma unroll
+              for (int u = 0; u < KR; ++u) acc[i] = fmaf(wj[u], f[u], acc[i]);
+            }
           }
         }
       }
@@ -256,7 +286,7 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
   if (pv_active) {
 #pragma unroll
     for (int i = 0; i < kAttnMaxVPerThread; ++i) {
-      const int d = d0 + i * kAttnThreads;
+      const int d = d0 + i * dstep;
       if (d < a.V) ov[my_group * a.V + d] = acc[i];
     }
   }
@@ -596,7 +626,7 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
   if (rows <= 0) return DLI_OK;
   AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v,
             ldv ? ldv : V, splits, part};
-  const int groups = V >= kAttnThreads ? 1 : kAttnThreads / V;
+  const int groups = attn_value_groups(V, ldv ? ldv : V);
   const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
   DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
